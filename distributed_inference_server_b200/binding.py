@@ -36,9 +36,11 @@ class EngineConfig(C.Structure):
 
 MIX_LIGHTNING, MIX_MINGRU, MIX_LATENT, MIX_ATTENTION, MIX_PARALLEL = range(5)
 MLP_NONE, MLP_DENSE, MLP_MOE = range(3)
-ACT_CLAMPED, ACT_GELU_TANH = range(2)
-NORM_RMS_SCALAR, NORM_LAYER = range(2)
+ACT_CLAMPED, ACT_GELU_TANH, ACT_SILU = range(3)
+NORM_RMS_SCALAR, NORM_LAYER, NORM_RMS = range(3)
+ROUTE_SOFTMAX_TOP, ROUTE_SIGMOID_GROUPS = range(2)
 ATTN_SIGMOID, ATTN_QK_NORM, ATTN_V_IS_K, ATTN_ROT_V, ATTN_BIAS = 1, 2, 4, 8, 16
+ATTN_BIAS_QKV, ATTN_QK_NORM_HEAD, ATTN_SINK, ATTN_GATE = 32, 64, 128, 256
 
 
 class LayerConfig(C.Structure):
@@ -48,14 +50,15 @@ class LayerConfig(C.Structure):
                [("kv_heads", C.c_int32), ("attn_flags", C.c_uint32), ("rot_factor", C.c_float), ("rot_low", C.c_float),
                 ("rot_high", C.c_float), ("rot_original", C.c_int32)] + \
                [(n, C.c_int32) for n in ("gla_heads", "gla_dim", "gla_vdim", "gla_rank")] + \
-               [("gla_tau", C.c_float), ("mix_scale", C.c_float), ("gla_scale", C.c_float), ("mlp_act", C.c_int32)]
+               [("gla_tau", C.c_float), ("mix_scale", C.c_float), ("gla_scale", C.c_float), ("mlp_act", C.c_int32)] + \
+               [(n, C.c_int32) for n in ("mask_chunk", "route_kind", "route_groups", "route_keep", "shared_ff")]
 
 
 class StackConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("vocab", "width", "n_layers", "canon_taps", "max_ctx", "max_logit_rows", "compute_dtype")] + \
                [("norm_eps", C.c_float), ("layers", C.POINTER(LayerConfig))] + \
                [("norm_kind", C.c_int32), ("embed_scale", C.c_float), ("logit_scale", C.c_float)] + \
-               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times")]
+               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times")] + [("logit_softcap", C.c_float)]
 
 
 class SamplingParams(C.Structure):

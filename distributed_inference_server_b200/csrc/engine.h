@@ -174,7 +174,10 @@ struct Engine {
   int stack_lat_split = 1, stack_lat_keys = 0;  // slicing of the history in latent attention for the pass being built
   int stack_abq = 0;          // tokens per query block of paged attention (0: the model has none); smallest over its layers
   int stack_kb = 0;           // its query blocks in the pass being built
-  int stack_att_split = 1, stack_att_keys = 0;  // its slicing of the history
+  int stack_att_split = 1, stack_att_keys = 0;  // its slicing of the history (layers without a chunked mask)
+  std::vector<std::pair<int, int>> stack_att_plan;  // per layer: (slices, keys per slice) of paged attention in the pass being built;
+                                                    // a chunked mask bounds the history a block walks, so its layers slice on their own
+  std::map<std::vector<uint64_t>, uint64_t> stack_graph_ids;  // (pass shape, slicing of every layer) -> key into `graphs`
   int stack_att_heads = 0, stack_att_groups = 0;  // most query heads, fewest key/value heads of an attention layer
   size_t stack_att_rec = 0;   // floats of one token's slice record: max over layers of heads * (vdim + 2)
   int stack_lat_heads = 0;    // most heads of a latent layer

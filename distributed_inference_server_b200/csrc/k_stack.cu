@@ -259,7 +259,8 @@ cudaError_t launch_stack_final_norm(const float *x, const int *row_map, const fl
 // cat (when given) receives [x ; x0] in the compute type (input of the projection in front of a loop pass);
 // h = (x - mean(x)) / sqrt(var(x) + eps) * pre_w + pre_b goes to hn (fp32, when given) and hc (compute type, when given).
 // The variance is the mean of the squared deviations from the mean (second pass over the row), all in fp32.
-template <bool F32>
+// RMS: the norms are v / sqrt(mean(v^2) + eps) * w instead -- no mean is taken off and there is no bias vector.
+template <bool F32, bool RMS>
 __global__ void __launch_bounds__(256) stack_boundary_ln_kernel(float *x, const float *y, int n_part, long long stride, const float *bias,
                                                                 const float *post_w, const float *post_b, const float *pre_w,
                                                                 const float *pre_b, float *hn, void *hc, const float *x0, void *cat,
@@ -274,14 +275,17 @@ __global__ void __launch_bounds__(256) stack_boundary_ln_kernel(float *x, const 
       float v = bias ? bias[i] : 0.f;
       for (int k = 0; k < n_part; k++) v += y[(long long)k * stride + t * W + i];
       row[i] = v;
-      s += v;
+      s += RMS ? v * v : v;
     }
-    const float mean = block_sum(s, sh) / (float)W;
-    float q = 0.f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = row[i] - mean; q += dvi * dvi; }
+    float mean = 0.f, q = 0.f;
+    if (RMS) q = s;
+    else {
+      mean = block_sum(s, sh) / (float)W;
+      for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = row[i] - mean; q += dvi * dvi; }
+    }
     const float r = rsqrtf(block_sum(q, sh) / (float)W + eps);
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      const float v = xr[i] + ((row[i] - mean) * r * post_w[i] + post_b[i]);
+      const float v = xr[i] + ((row[i] - mean) * r * post_w[i] + (RMS ? 0.f : post_b[i]));
       xr[i] = v;
       row[i] = v;
     }
@@ -296,46 +300,59 @@ __global__ void __launch_bounds__(256) stack_boundary_ln_kernel(float *x, const 
   }
   if (!pre_w) return;
   float s = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];  // each thread re-reads what it wrote itself
-  const float mean = block_sum(s, sh) / (float)W;
-  float q = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = row[i] - mean; q += dvi * dvi; }
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += RMS ? row[i] * row[i] : row[i];  // each thread re-reads what it wrote itself
+  float mean = 0.f, q = 0.f;
+  if (RMS) q = s;
+  else {
+    mean = block_sum(s, sh) / (float)W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = row[i] - mean; q += dvi * dvi; }
+  }
   const float r = rsqrtf(block_sum(q, sh) / (float)W + eps);
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float h = (row[i] - mean) * r * pre_w[i] + pre_b[i];
+    const float h = (row[i] - mean) * r * pre_w[i] + (RMS ? 0.f : pre_b[i]);
     if (hn) hn[t * W + i] = h;
     if (hc) st_el<F32>(hc, t * W + i, h);
   }
 }
 cudaError_t launch_stack_boundary_ln(float *x, const float *y, int n_part, long long stride, const float *bias, const float *post_w,
                                      const float *post_b, const float *pre_w, const float *pre_b, float *hn, void *hc, const float *x0,
-                                     void *cat, bool f32, int T, int W, float eps, cudaStream_t st) {
+                                     void *cat, bool f32, int T, int W, float eps, bool rms, cudaStream_t st) {
   if ((size_t)W * 4 > 160 * 1024) return cudaErrorInvalidValue;
   if (T <= 0) return cudaSuccess;
   static DeviceOnce once;
   DIS_CUDA_TRY(once.run([&] {
-    cudaError_t e = cudaFuncSetAttribute(stack_boundary_ln_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_boundary_ln_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(stack_boundary_ln_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_boundary_ln_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_boundary_ln_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_boundary_ln_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
   }));
   const size_t shb = (size_t)W * 4;
-  if (f32) stack_boundary_ln_kernel<true><<<T, 256, shb, st>>>(x, y, n_part, stride, bias, post_w, post_b, pre_w, pre_b, hn, hc, x0, cat, W, eps);
-  else stack_boundary_ln_kernel<false><<<T, 256, shb, st>>>(x, y, n_part, stride, bias, post_w, post_b, pre_w, pre_b, hn, hc, x0, cat, W, eps);
+#define DIS_BOUNDARY(F, R) \
+  stack_boundary_ln_kernel<F, R><<<T, 256, shb, st>>>(x, y, n_part, stride, bias, post_w, post_b, pre_w, pre_b, hn, hc, x0, cat, W, eps)
+  if (f32 && rms) DIS_BOUNDARY(true, true);
+  else if (f32) DIS_BOUNDARY(true, false);
+  else if (rms) DIS_BOUNDARY(false, true);
+  else DIS_BOUNDARY(false, false);
+#undef DIS_BOUNDARY
   return cudaGetLastError();
 }
 
+// b == null: the RMS form, x / sqrt(mean(x^2) + eps) * w
 template <bool F32>
 __global__ void stack_final_ln_kernel(const float *x, const int *row_map, const float *w, const float *b, void *out, int W, float eps,
                                       float scale) {
   __shared__ float sh[32];
   const long long r = blockIdx.x;
   const float *xr = x + (long long)(row_map ? row_map[r] : r) * W;
-  float s = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) s += xr[i];
-  const float mean = block_sum(s, sh) / (float)W;
-  float q = 0.f;
+  float mean = 0.f, q = 0.f;
+  if (b) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) s += xr[i];
+    mean = block_sum(s, sh) / (float)W;
+  }
   for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = xr[i] - mean; q += dvi * dvi; }
   const float k = rsqrtf(block_sum(q, sh) / (float)W + eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(out, r * W + i, ((xr[i] - mean) * k * w[i] + b[i]) * scale);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(out, r * W + i, ((xr[i] - mean) * k * w[i] + (b ? b[i] : 0.f)) * scale);
 }
 cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const float *w, const float *b, void *out, bool f32, int R, int W,
                                   float eps, float scale, cudaStream_t st) {
@@ -350,6 +367,16 @@ __global__ void stack_scale_kernel(float *v, long long n, float s) {
 cudaError_t launch_stack_scale(float *v, long long n, float s, cudaStream_t st) {
   if (n <= 0) return cudaSuccess;
   stack_scale_kernel<<<(int)std::min<long long>((n + 255) / 256, 148 * 8), 256, 0, st>>>(v, n, s);
+  return cudaGetLastError();
+}
+
+__global__ void stack_softcap_kernel(float *v, long long n, float cap, float inv) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    v[i] = cap * tanhf(v[i] * inv);
+}
+cudaError_t launch_stack_softcap(float *v, long long n, float cap, cudaStream_t st) {
+  if (n <= 0 || !(cap > 0.f)) return cudaSuccess;
+  stack_softcap_kernel<<<(int)std::min<long long>((n + 255) / 256, 148 * 8), 256, 0, st>>>(v, n, cap, 1.f / cap);
   return cudaGetLastError();
 }
 
@@ -496,6 +523,7 @@ __global__ void stack_glu_kernel(const float *__restrict__ gu, int n_part, long 
       for (int k = 1; k < n_part; k++) { g += gr[(long long)k * stride + c]; u += gr[(long long)k * stride + ff + c]; }
       float v;
       if (ACT == DIS_ACT_GELU_TANH) v = gelu_tanh_(g) * u;
+      else if (ACT == DIS_ACT_SILU) v = g * sigmoid_precise(g) * u;
       else {
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
@@ -513,6 +541,9 @@ cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, cons
   if (kind == DIS_ACT_GELU_TANH) {
     if (f32) stack_glu_kernel<true, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
     else stack_glu_kernel<false, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
+  } else if (kind == DIS_ACT_SILU) {
+    if (f32) stack_glu_kernel<true, DIS_ACT_SILU><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
+    else stack_glu_kernel<false, DIS_ACT_SILU><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
   } else {
     if (f32) stack_glu_kernel<true, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
     else stack_glu_kernel<false, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
@@ -522,30 +553,87 @@ cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, cons
 
 // ------------------------------------------------------------------------------------------------ router and expert rows
 // One block of four warps per token: the warps share the experts' fp32 logits against the fp32 router matrix (a warp per expert
-// at a time), then the first warp runs `top` rounds of arg-max (lowest index wins a tie) and the softmax over the chosen
-// logits.  E <= 1024 (logits sit in shared memory).
+// at a time), then the first warp chooses.  E <= 1024 (logits sit in shared memory).
+// DIS_ROUTE_SOFTMAX_TOP: `top` rounds of arg-max over the logits (lowest index wins a tie), weights = softmax over the chosen.
+// DIS_ROUTE_SIGMOID_GROUPS: s = sigmoid(z); choice scores c = s + correction; with groups > 1 the experts form `groups` equal
+// contiguous runs, a run is ranked by the sum of its top two c, and every expert outside the `keep` best runs gets
+// c = -inf; `top` rounds of arg-max over c; weights = the chosen s over their sum (+ 1e-20).
+// extra (or null): one more fp32 row [W] whose product with the token lands in extra_out[t] (the logit of a per-token gate).
 template <bool F32>
 __global__ void __launch_bounds__(128) stack_route_kernel(const void *hc, const float *__restrict__ router, int T, int W, int E, int top,
-                                                          int *idx, float *wt) {
-  extern __shared__ float zs[];  // [E]
+                                                          int kind, const float *__restrict__ correction, int groups, int keep,
+                                                          const float *__restrict__ extra, float *extra_out, int *idx, float *wt) {
+  extern __shared__ float zs[];  // [E] logits (sigmoid scores), [E] choice scores, [groups] run scores, [groups] kept flags
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   const int t = blockIdx.x;
-  float *z = zs;
-  for (int e = w; e < E; e += 4) {
+  float *z = zs, *c = zs + E, *gs = c + E;
+  for (int e = w; e < E + (extra ? 1 : 0); e += 4) {
+    const float *wr = e < E ? router + (long long)e * W : extra;
     float s = 0.f;
 #pragma unroll 4
-    for (int i = l; i < W; i += 32) s = fmaf(ld_el<F32>(hc, (long long)t * W + i), router[(long long)e * W + i], s);
+    for (int i = l; i < W; i += 32) s = fmaf(ld_el<F32>(hc, (long long)t * W + i), wr[i], s);
     s = warp_sum(s);
-    if (l == 0) z[e] = s;
+    if (l == 0) {
+      if (e < E) z[e] = s;
+      else extra_out[t] = s;
+    }
   }
   __syncthreads();
+  const bool sig = kind == DIS_ROUTE_SIGMOID_GROUPS;
+  if (sig) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const float sv = sigmoid_precise(z[e]);
+      z[e] = sv;
+      c[e] = sv + correction[e];
+    }
+    __syncthreads();
+    if (groups > 1 && keep < groups) {
+      const int per = E / groups;
+      for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        float a = -INFINITY, b = -INFINITY;  // the two largest of the run
+        for (int j = 0; j < per; j++) {
+          const float v = c[g * per + j];
+          if (v > a) { b = a; a = v; }
+          else if (v > b) b = v;
+        }
+        gs[g] = per > 1 ? a + b : a;
+      }
+      __syncthreads();
+      int *kept = reinterpret_cast<int *>(gs + groups);  // [groups]
+      for (int g = threadIdx.x; g < groups; g += blockDim.x) kept[g] = 0;
+      __syncthreads();
+      if (w == 0) {
+        for (int k = 0; k < keep; k++) {  // keep rounds of arg-max over the runs not yet kept (lowest index wins a tie)
+          float best = -INFINITY;
+          int bi = 0x7fffffff;
+          for (int g = l; g < groups; g += 32) {
+            const float v = gs[g];
+            if (!kept[g] && (v > best || (v == best && g < bi))) { best = v; bi = g; }
+          }
+          for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+          }
+          if (l == 0 && bi != 0x7fffffff) kept[bi] = 1;
+          __syncwarp();
+        }
+      }
+      __syncthreads();
+      for (int e = threadIdx.x; e < E; e += blockDim.x)
+        if (!kept[e / per]) c[e] = -INFINITY;
+      __syncthreads();
+    }
+  }
   if (w != 0) return;
+  const float *score = sig ? c : z;
+  float *taken = sig ? c : z;
   float m0 = 0.f, den = 0.f, mine = 0.f;
   for (int k = 0; k < top; k++) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = l; e < E; e += 32) {
-      const float v = z[e];
+      const float v = score[e];
       if (v > best || (v == best && e < bi)) { best = v; bi = e; }
     }
     for (int o = 16; o > 0; o >>= 1) {
@@ -553,22 +641,26 @@ __global__ void __launch_bounds__(128) stack_route_kernel(const void *hc, const 
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
+    if (bi == 0x7fffffff) bi = 0;  // nothing left to choose from (the configuration check rules it out)
     if (k == 0) m0 = best;
-    const float p = expf(best - m0);
+    const float p = sig ? z[bi] : expf(best - m0);
     den += p;
     if (l == k % 32) mine = p;  // lane k keeps the k-th weight (top <= 32)
-    if (l == 0) { idx[(long long)t * top + k] = bi; z[bi] = -INFINITY; }
+    __syncwarp();
+    if (l == 0) { idx[(long long)t * top + k] = bi; taken[bi] = -INFINITY; }
     __syncwarp();
   }
-  if (l < top) wt[(long long)t * top + l] = mine / den;
+  if (l < top) wt[(long long)t * top + l] = sig ? mine / (den + 1e-20f) : mine / den;
 }
-cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int *idx, float *wt,
+cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int kind,
+                               const float *correction, int groups, int keep, const float *extra, float *extra_out, int *idx, float *wt,
                                cudaStream_t st) {
   if (E > 1024 || top > 32 || top > E) return cudaErrorInvalidValue;
+  if (kind == DIS_ROUTE_SIGMOID_GROUPS && (!correction || groups < 0 || (groups > 1 && (E % groups || keep < 1)))) return cudaErrorInvalidValue;
   if (T <= 0) return cudaSuccess;
-  const size_t sh = (size_t)E * sizeof(float);
-  if (f32) stack_route_kernel<true><<<T, 128, sh, st>>>(hc, router, T, W, E, top, idx, wt);
-  else stack_route_kernel<false><<<T, 128, sh, st>>>(hc, router, T, W, E, top, idx, wt);
+  const size_t sh = (size_t)(2 * E + 2 * std::max(groups, 1)) * sizeof(float);
+  if (f32) stack_route_kernel<true><<<T, 128, sh, st>>>(hc, router, T, W, E, top, kind, correction, groups, keep, extra, extra_out, idx, wt);
+  else stack_route_kernel<false><<<T, 128, sh, st>>>(hc, router, T, W, E, top, kind, correction, groups, keep, extra, extra_out, idx, wt);
   return cudaGetLastError();
 }
 
@@ -622,17 +714,22 @@ cudaError_t launch_stack_moe_gather(const void *hc, const int *perm_tok, void *x
   return cudaGetLastError();
 }
 
-__global__ void stack_moe_combine_kernel(const float *rows, const int *where, const float *wt, float *y, int W, int top) {
+// y = sum_k wt_k * (row of choice k) [+ sigmoid(shared_gate[t]) * shared[t]]: the shared expert's output, when there is one,
+// joins here behind its per-token gate
+__global__ void stack_moe_combine_kernel(const float *rows, const int *where, const float *wt, const float *shared,
+                                         const float *shared_gate, float *y, int W, int top) {
   const long long t = blockIdx.x;
+  const float sg = shared ? sigmoid_precise(shared_gate[t]) : 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < top; k++) s = fmaf(wt[t * top + k], rows[(long long)where[t * top + k] * W + i], s);
+    if (shared) s = fmaf(sg, shared[t * W + i], s);
     y[t * W + i] = s;
   }
 }
-cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, float *y, int T, int W, int top,
-                                     cudaStream_t st) {
-  stack_moe_combine_kernel<<<T, 256, 0, st>>>(rows, where, wt, y, W, top);
+cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, const float *shared,
+                                     const float *shared_gate, float *y, int T, int W, int top, cudaStream_t st) {
+  stack_moe_combine_kernel<<<T, 256, 0, st>>>(rows, where, wt, shared, shared_gate, y, W, top);
   return cudaGetLastError();
 }
 

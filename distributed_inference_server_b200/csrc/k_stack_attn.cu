@@ -1,29 +1,32 @@
 // k_stack_attn.cu -- grouped-query attention over paged keys and values for the layer-list decoders (DIS_MIX_ATTENTION and the
-// attention half of DIS_MIX_PARALLEL): the per-token preparation (biases, whole-projection query/key norm, partial rotary with a
-// frequency table, cache write of the rotated keys and of the values -- own projection or the unrotated keys, optionally
-// rotated by their position) and the attention itself with softmax or per-head sigmoid weights, over the whole history or a
-// slice of it.  Scores, weights, norms and angles are fp32 (angles are formed in double) whatever the cache's element type.
+// attention half of DIS_MIX_PARALLEL): the per-token preparation (biases, whole-projection or per-head query/key norm, partial
+// rotary with a frequency table, cache write of the rotated keys and of the values -- own projection or the unrotated keys,
+// optionally rotated by their position; a layer that reads another layer's cache writes nothing) and the attention itself with
+// softmax (optionally with a per-head sink logit in the denominator) or per-head sigmoid weights, under a causal mask that may
+// be cut into chunks of positions, over the whole visible history or a slice of it, with an optional per-head sigmoid gate on
+// the output.  Scores, weights, norms and angles are fp32 (angles are formed in double) whatever the cache's element type.
 #include "stack_dev.cuh"
 
 namespace dis {
 
 // ------------------------------------------------------------------------------------------------ preparation
 // One block per token.  proj row: queries at q_off [H][d], keys at k_off [G][d], values at v_off [G][dv] (unless values are
-// the keys).  `bias` (or null): [H*d + G*d] for q | k, added here when the product left it out.
+// the keys).  `bias` (or null): one entry per column of the projection, added here when the product left it out.
+// kpool == null: the layer reads another layer's cache; only the queries are prepared.
 template <bool F32>
 __global__ void __launch_bounds__(128) stack_attn_prep_kernel(const float *proj, long long ld, int q_off, int k_off, int v_off,
                                                               const float *bias, const float *qn, const float *kn, const double *freq,
                                                               const double *vfreq, StackAttn c, StackSpans sp, float *qf, void *kpool,
                                                               void *vpool, float *vrot, const int *page_table, int max_pages,
                                                               int page_size) {
-  extern __shared__ float tab[];  // cos [half], sin [half], value cos [dv/2], value sin [dv/2]
+  extern __shared__ float tab[];  // cos [half], sin [half], value cos [dv/2], value sin [dv/2], per-head factors [H + G]
   __shared__ float sh[32];
   const int t = blockIdx.x;
   const float *row = proj + (long long)t * ld;
   const int pos = sp.pos[t], slot = sp.slot[t];
   const int half = c.rot_dims >> 1, vhalf = c.dv >> 1;
-  const bool rot_v = (c.flags & DIS_ATTN_ROT_V) != 0;
-  float *cs = tab, *sn = tab + half, *vcs = sn + half, *vsn = vcs + vhalf;
+  const bool rot_v = (c.flags & DIS_ATTN_ROT_V) != 0, own = kpool != nullptr;
+  float *cs = tab, *sn = tab + half, *vcs = sn + half, *vsn = vcs + vhalf, *hr = vsn + vhalf;
   // the angle pos * f is formed and brought into [-pi, pi] in double (position 100000 is then as exact as position 5); sine and
   // cosine of the reduced angle are float
   auto angle = [](int p, double f, float *sn_out, float *cs_out) {
@@ -41,7 +44,8 @@ __global__ void __launch_bounds__(128) stack_attn_prep_kernel(const float *proj,
       vrot[(long long)t * c.dv + vhalf + i] = s_;
     }
   const int nq = c.H * c.d, nk = c.G * c.d;
-  const float *qb = bias, *kb = bias ? bias + nq : nullptr;
+  const float *qb = bias ? bias + q_off : nullptr, *kb = bias ? bias + k_off : nullptr, *vb = bias ? bias + v_off : nullptr;
+  const bool head_norm = (c.flags & DIS_ATTN_QK_NORM_HEAD) != 0;
   float rq = 1.f, rk = 1.f;
   if (c.flags & DIS_ATTN_QK_NORM) {
     float s = 0.f;
@@ -50,32 +54,46 @@ __global__ void __launch_bounds__(128) stack_attn_prep_kernel(const float *proj,
     s = 0.f;
     for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = row[k_off + i] + (kb ? kb[i] : 0.f); s += v * v; }
     rk = rsqrtf(block_sum(s, sh) / (float)nk + c.eps);
+  } else if (head_norm) {  // one factor per head: a warp per head at a time, query heads then key heads
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    for (int h = w; h < c.H + (own ? c.G : 0); h += (int)(blockDim.x >> 5)) {
+      const bool isq = h < c.H;
+      const int off = isq ? q_off + h * c.d : k_off + (h - c.H) * c.d;
+      const float *b = isq ? (qb ? qb + h * c.d : nullptr) : (kb ? kb + (h - c.H) * c.d : nullptr);
+      float s = 0.f;
+      for (int i = l; i < c.d; i += 32) { const float v = row[off + i] + (b ? b[i] : 0.f); s += v * v; }
+      s = warp_sum(s);
+      if (l == 0) hr[h] = rsqrtf(s / (float)c.d + c.eps);
+    }
   }
   __syncthreads();
-  auto val = [&](int off, const float *b, const float *g, float r, int i) {
+  // g: the gain vector (whole projection, or [d] shared by the heads); r / rh: the factor of the projection or of each head
+  auto val = [&](int off, const float *b, const float *g, float r, const float *rh, int i) {
     float v = row[off + i] + (b ? b[i] : 0.f);
-    if (g) v = v * r * g[i];
+    if (g) v = head_norm ? v * rh[i / c.d] * g[i % c.d] : v * r * g[i];
     return v;
   };
-  auto rotated = [&](int off, const float *b, const float *g, float r, int i) {
+  auto rotated = [&](int off, const float *b, const float *g, float r, const float *rh, int i) {
     const int e = i % c.d;
-    if (e >= c.rot_dims) return val(off, b, g, r, i);
-    if (e < half) return val(off, b, g, r, i) * cs[e] - val(off, b, g, r, i + half) * sn[e];
-    return val(off, b, g, r, i) * cs[e - half] + val(off, b, g, r, i - half) * sn[e - half];
+    if (e >= c.rot_dims) return val(off, b, g, r, rh, i);
+    if (e < half) return val(off, b, g, r, rh, i) * cs[e] - val(off, b, g, r, rh, i + half) * sn[e];
+    return val(off, b, g, r, rh, i) * cs[e - half] + val(off, b, g, r, rh, i - half) * sn[e - half];
   };
-  const float *qg = (c.flags & DIS_ATTN_QK_NORM) ? qn : nullptr, *kg = (c.flags & DIS_ATTN_QK_NORM) ? kn : nullptr;
-  for (int i = threadIdx.x; i < nq; i += blockDim.x) qf[(long long)t * nq + i] = rotated(q_off, qb, qg, rq, i);
+  const bool normed = (c.flags & (DIS_ATTN_QK_NORM | DIS_ATTN_QK_NORM_HEAD)) != 0;
+  const float *qg = normed ? qn : nullptr, *kg = normed ? kn : nullptr;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) qf[(long long)t * nq + i] = rotated(q_off, qb, qg, rq, hr, i);
+  if (!own) return;
   const long long prow = (long long)page_table[(long long)slot * max_pages + pos / page_size] * page_size + pos % page_size;
-  for (int i = threadIdx.x; i < nk; i += blockDim.x) st_el<F32>(kpool, prow * nk + i, rotated(k_off, kb, kg, rk, i));
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) st_el<F32>(kpool, prow * nk + i, rotated(k_off, kb, kg, rk, hr + c.H, i));
   const int nv = c.G * c.dv;
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     float v;
     if (c.flags & DIS_ATTN_V_IS_K) v = row[k_off + i] + (kb ? kb[i] : 0.f);  // dv == d: the keys as projected
-    else if (!rot_v) v = row[v_off + i];
+    else if (!rot_v) v = row[v_off + i] + (vb ? vb[i] : 0.f);
     else {
       const int e = i % c.dv;
-      v = e < vhalf ? row[v_off + i] * vcs[e] - row[v_off + i + vhalf] * vsn[e]
-                    : row[v_off + i] * vcs[e - vhalf] + row[v_off + i - vhalf] * vsn[e - vhalf];
+      auto vv = [&](int j) { return row[v_off + j] + (vb ? vb[j] : 0.f); };
+      v = e < vhalf ? vv(i) * vcs[e] - vv(i + vhalf) * vsn[e] : vv(i) * vcs[e - vhalf] + vv(i - vhalf) * vsn[e - vhalf];
     }
     st_el<F32>(vpool, prow * nv + i, v);
   }
@@ -85,7 +103,7 @@ cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, i
                                    float *qf, void *kpool, void *vpool, float *vrot, bool f32, const int *page_table, int max_pages,
                                    int page_size, cudaStream_t st) {
   if (sp.T <= 0) return cudaSuccess;
-  const size_t sh = (size_t)(c.rot_dims + c.dv) * sizeof(float);
+  const size_t sh = (size_t)(c.rot_dims + c.dv + c.H + c.G) * sizeof(float);
   if (f32) stack_attn_prep_kernel<true><<<sp.T, 128, sh, st>>>(proj, ld, q_off, k_off, v_off, bias, qn, kn, freq, vfreq, c, sp, qf, kpool, vpool, vrot, page_table, max_pages, page_size);
   else stack_attn_prep_kernel<false><<<sp.T, 128, sh, st>>>(proj, ld, q_off, k_off, v_off, bias, qn, kn, freq, vfreq, c, sp, qf, kpool, vpool, vrot, page_table, max_pages, page_size);
   return cudaGetLastError();
@@ -107,7 +125,13 @@ struct AttnOut {
   int off;
   float scale;        // factor on the output (weight of this mixer inside a parallel layer)
   const float *vrot;  // [T][dv]: cos | sin of the query position's value angles, or null
+  const float *gate;  // [T][ldg]: logit of head h's output gate at column h, or null
+  long long ldg;
 };
+// factor on head h's output at token tok: the mixer's weight times the head's sigmoid gate
+__device__ __forceinline__ float attn_out_factor(const AttnOut &o, int tok, int h) {
+  return o.gate ? o.scale * sigmoid_precise(o.gate[(long long)tok * o.ldg + h]) : o.scale;
+}
 
 template <bool F32>
 __device__ __forceinline__ void attn_store(const AttnOut &o, const float *a, float inv, int tok, int h, int dv, int j) {
@@ -117,7 +141,7 @@ __device__ __forceinline__ void attn_store(const AttnOut &o, const float *a, flo
     const float *cs = o.vrot + (long long)tok * dv, *sn = cs + hf;
     v = j < hf ? (a[j] * cs[j] + a[j + hf] * sn[j]) * inv : (a[j] * cs[j - hf] - a[j - hf] * sn[j - hf]) * inv;
   }
-  st_el<F32>(o.out, (long long)tok * o.ld + o.off + (long long)h * dv + j, v * o.scale);
+  st_el<F32>(o.out, (long long)tok * o.ld + o.off + (long long)h * dv + j, v * attn_out_factor(o, tok, h));
 }
 
 int stack_attn_block_tokens(const StackAttn &c, bool f32) {
@@ -134,7 +158,7 @@ static size_t attn_smem(const StackAttn &c, int bq) {
 
 template <bool F32, bool SIG>
 __global__ void __launch_bounds__(kAtWarps * 32) stack_attn_kernel(const float *qf, const void *kpool, const void *vpool, const float *temp,
-                                                                   const float *pb, StackAttn c, StackSpans sp, const int *qb_tok0,
+                                                                   const float *pb, const float *sink, StackAttn c, StackSpans sp, const int *qb_tok0,
                                                                    const int *qb_len, const int *page_table, int max_pages,
                                                                    int page_size, AttnOut o, int keys_per_split, float *part) {
   extern __shared__ float shm[];
@@ -156,9 +180,11 @@ __global__ void __launch_bounds__(kAtWarps * 32) stack_attn_kernel(const float *
     qs[i] = qf[((long long)(tok0 + p / R) * c.H + g * R + p % R) * d + e];
   }
   for (int i = threadIdx.x; i < pairs * dv; i += blockDim.x) acc[i] = 0.f;
-  for (int i = threadIdx.x; i < pairs; i += blockDim.x) { mx[i] = -INFINITY; dn[i] = 0.f; }
+  const bool with_sink = !SIG && sink && blockIdx.z == 0;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) { mx[i] = with_sink ? sink[g * R + i % R] : -INFINITY; dn[i] = with_sink ? 1.f : 0.f; }
   const int *pt = page_table + (long long)slot * max_pages;
-  const int k_begin = part ? (int)blockIdx.z * keys_per_split : 0;
+  const int k_lo = c.chunk > 0 ? sp.pos[tok0] / c.chunk * c.chunk : 0;
+  const int k_begin = part ? k_lo + (int)blockIdx.z * keys_per_split : k_lo;
   const int k_end = part ? min(last_pos + 1, k_begin + keys_per_split) : last_pos + 1;
   const long long krow = (long long)c.G * d, vrow = (long long)c.G * dv;
   for (int k0 = k_begin; k0 < k_end; k0 += kAtTile) {
@@ -177,9 +203,10 @@ __global__ void __launch_bounds__(kAtWarps * 32) stack_attn_kernel(const float *
     __syncthreads();
     for (int p = w; p < pairs; p += kAtWarps) {
       const int qpos = sp.pos[tok0 + p / R], h = g * R + p % R;
+      const int qlo = c.chunk > 0 ? qpos / c.chunk * c.chunk : 0;
       const float *q = qs + (size_t)p * d;
       float sc = -INFINITY;
-      if (l < nk && k0 + l <= qpos) {
+      if (l < nk && k0 + l <= qpos && k0 + l >= qlo) {
         const float *kr = kt + (size_t)l * DP;
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // four chains, added at the end: the sum's order is fixed by d alone
         int i = 0;
@@ -197,7 +224,7 @@ __global__ void __launch_bounds__(kAtWarps * 32) stack_attn_kernel(const float *
         const float m_old = mx[p];
         m_new = fmaxf(m_old, warp_max(sc));
         pr = sc == -INFINITY ? 0.f : expf(sc - m_new);
-        corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+        corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);  // (m_new is -inf too while a pair has seen nothing: pr = 0 then)
         psum = warp_sum(pr);
       }
       float *a = acc + (size_t)p * dv;
@@ -305,17 +332,19 @@ __device__ __forceinline__ float ex2_(float x) {  // 2^x, flushing results below
 }
 
 // Scores of one 64-key tile -> sigmoid weights, or scaled scores and the rows' running maxima (softmax).  MASKED: the tile
-// reaches past a row's position or the slice's end, so every element is checked; interior tiles skip the checks.
+// reaches past a row's position or the slice's end, or starts before a row's chunk, so every element is checked; interior tiles
+// skip the checks.
 template <bool SIG, bool MASKED>
 __device__ __forceinline__ void attn_tile_weights(float (&sacc)[kMmKeys / 8][4], float (&mnew)[2], int k0, int qd, const int (&r_pos)[2],
-                                                  int k_end, const float (&tmp_h)[2], const float (&pb_h)[2], float scale2) {
+                                                  const int (&r_lo)[2], int k_end, const float (&tmp_h)[2], const float (&pb_h)[2],
+                                                  float scale2) {
 #pragma unroll
   for (int j = 0; j < kMmKeys / 8; j++)
 #pragma unroll
     for (int q4 = 0; q4 < 4; q4++) {
       const int e = q4 >> 1;
       bool vis = true;
-      if (MASKED) { const int kp = k0 + j * 8 + qd * 2 + (q4 & 1); vis = kp <= r_pos[e] && kp < k_end; }
+      if (MASKED) { const int kp = k0 + j * 8 + qd * 2 + (q4 & 1); vis = kp <= r_pos[e] && kp < k_end && kp >= r_lo[e]; }
       float sv = sacc[j][q4];
       if (SIG) {
         float rc;
@@ -334,7 +363,7 @@ int stack_attn_mma_block_tokens(const StackAttn &c) { return std::max(1, kMmRows
 template <int DMAX, bool SIG>
 __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const float *__restrict__ qf, const uint16_t *__restrict__ kpool,
                                                                        const uint16_t *__restrict__ vpool, const float *temp,
-                                                                       const float *pb, StackAttn c, StackSpans sp, const int *qb_tok0,
+                                                                       const float *pb, const float *sink, StackAttn c, StackSpans sp, const int *qb_tok0,
                                                                        const int *qb_len, const int *page_table, int max_pages,
                                                                        int page_size, AttnOut o, int keys_per_split, float *part) {
   constexpr int PITCH = DMAX + 8;  // elements per shared row: 16-byte rows land in distinct bank groups
@@ -349,14 +378,16 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, qd = lane & 3;
   const int slot = sp.slot[tok0], pos_first = sp.pos[tok0], last_pos = pos_first + nq - 1;
   const int *pt = page_table + (long long)slot * max_pages;
-  const int k_begin = part ? (int)blockIdx.z * keys_per_split : 0;
+  // chunked mask: the first token's chunk is where the block's history starts (later rows may start later still)
+  const int k_lo = c.chunk > 0 ? pos_first / c.chunk * c.chunk : 0;
+  const int k_begin = part ? k_lo + (int)blockIdx.z * keys_per_split : k_lo;
   const int k_end = part ? min(last_pos + 1, k_begin + keys_per_split) : last_pos + 1;
   const int nk16 = (d + 15) >> 4, nv8 = dv >> 3, dc = d >> 3, vc = dv >> 3;  // k-steps of Q K^T, n-tiles of P V, 16-byte chunks per row
   // columns d .. 16 nk16 of the K stages are read by the last k-step: zero them once (cp.async never touches them)
   if (d & 15)
     for (int i = threadIdx.x; i < 2 * kMmKeys * 8; i += blockDim.x) Ks[(i >> 3) * PITCH + d + (i & 7)] = 0;
   // ---- this thread's rows: r0 = 16 warp + gid and r0 + 8
-  int r_tok[2], r_head[2], r_pos[2];
+  int r_tok[2], r_head[2], r_pos[2], r_lo[2];
   bool r_ok[2];
   uint32_t qa[DMAX / 16][4];
 #pragma unroll
@@ -366,6 +397,7 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
     r_tok[e] = tok0 + (r_ok[e] ? r / R : 0);
     r_head[e] = kvh * R + (r_ok[e] ? r % R : 0);
     r_pos[e] = r_ok[e] ? pos_first + r / R : -1;
+    r_lo[e] = c.chunk > 0 && r_ok[e] ? r_pos[e] / c.chunk * c.chunk : 0;
   }
 #pragma unroll
   for (int ks = 0; ks < DMAX / 16; ks++) {
@@ -388,6 +420,10 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
 #pragma unroll
   for (int j = 0; j < DMAX / 8; j++) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f; }
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+  if (!SIG && sink && blockIdx.z == 0) {  // the sink: the extra term of the denominator, entered once (first slice, one lane of the four)
+#pragma unroll
+    for (int e = 0; e < 2; e++) { mrow[e] = sink[r_head[e]] * kLog2e; lrow[e] = qd == 0 ? 1.f : 0.f; }
+  }
   float tmp_h[2] = {1.f, 1.f}, pb_h[2] = {0.f, 0.f};
   if (SIG) {
 #pragma unroll
@@ -396,6 +432,9 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
   const float scale2 = c.scale * kLog2e;
   const bool warp_live = warp * 16 < rows;
   const int warp_last_pos = pos_first + min(rows - 1, warp * 16 + 15) / R;
+  const int warp_first_pos = pos_first + (warp * 16) / R;
+  const int warp_lo = c.chunk > 0 ? warp_first_pos / c.chunk * c.chunk : 0;        // first key any row of the warp sees
+  const int warp_lo_max = c.chunk > 0 ? warp_last_pos / c.chunk * c.chunk : 0;     // first key every row of the warp sees
   const long long krow = (long long)c.G * d, vrow = (long long)c.G * dv;
   const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks), vs_base = (uint32_t)__cvta_generic_to_shared(Vs);
   // two threads per key row: one page-table read per thread and tile, then the row's 16-byte chunks alternate between the two
@@ -428,7 +467,7 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    if (warp_live && k0 <= warp_last_pos) {
+    if (warp_live && k0 <= warp_last_pos && k0 + kMmKeys > warp_lo) {
       // S = Q K^T: k-steps outside, key tiles inside, so that consecutive products go to different accumulators; one ldmatrix
       // brings the fragments of two key tiles (lane l: matrix l / 8 = (tile, column half), row l % 8)
       const uint32_t kt = ks_base + (uint32_t)(stage * kMmKeys * PITCH * 2);
@@ -449,10 +488,10 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
       }
       // ---- weights, fp32.  Scores are carried in units of log 2 (the factor 1 / ln 2 is folded into the scale), so every
       // exponential is one ex2.  Only a tile that reaches past a row's position or the slice's end needs the mask.
-      const bool masked = k0 + kMmKeys - 1 > pos_first + (warp * 16) / R || k0 + kMmKeys > k_end;
+      const bool masked = k0 + kMmKeys - 1 > warp_first_pos || k0 + kMmKeys > k_end || k0 < warp_lo_max;
       float mnew[2] = {mrow[0], mrow[1]};
-      if (masked) attn_tile_weights<SIG, true>(sacc, mnew, k0, qd, r_pos, k_end, tmp_h, pb_h, scale2);
-      else attn_tile_weights<SIG, false>(sacc, mnew, k0, qd, r_pos, k_end, tmp_h, pb_h, scale2);
+      if (masked) attn_tile_weights<SIG, true>(sacc, mnew, k0, qd, r_pos, r_lo, k_end, tmp_h, pb_h, scale2);
+      else attn_tile_weights<SIG, false>(sacc, mnew, k0, qd, r_pos, r_lo, k_end, tmp_h, pb_h, scale2);
       if (!SIG) {
         float corr[2];
 #pragma unroll
@@ -516,7 +555,7 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
 #pragma unroll
       for (int j = 0; j < DMAX / 8; j++)
         if (j < nv8) { ot[(gid + e * 8) * (dv + 1) + j * 8 + qd * 2] = oacc[j][e * 2]; ot[(gid + e * 8) * (dv + 1) + j * 8 + qd * 2 + 1] = oacc[j][e * 2 + 1]; }
-      if (qd == 0) ot[(gid + e * 8) * (dv + 1) + dv] = SIG ? o.scale : o.scale / lrow[e];
+      if (qd == 0) ot[(gid + e * 8) * (dv + 1) + dv] = attn_out_factor(o, r_tok[e], r_head[e]) * (SIG ? 1.f : 1.f / lrow[e]);
     }
     __syncwarp();
     const int hf = dv >> 1;
@@ -543,7 +582,7 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
       if (qd == 0) { rec[dv] = SIG ? 0.f : mrow[e] * kLn2; rec[dv + 1] = lrow[e]; }  // the maximum back in natural units
       continue;
     }
-    const float inv = SIG ? o.scale : o.scale / lrow[e];
+    const float inv = attn_out_factor(o, r_tok[e], r_head[e]) * (SIG ? 1.f : 1.f / lrow[e]);
     uint16_t *orow = reinterpret_cast<uint16_t *>(o.out) + (long long)r_tok[e] * o.ld + o.off + (long long)r_head[e] * dv;
 #pragma unroll
     for (int j = 0; j < DMAX / 8; j++)
@@ -552,10 +591,13 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
 }
 
 cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vpool, bool f32, const float *temp, const float *pb,
-                              const StackAttn &c, const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb, int bq,
-                              const int *page_table, int max_pages, int page_size, void *out, long long ld_out, int out_off,
-                              float out_scale, const float *vrot, int n_split, int keys_per_split, float *part, cudaStream_t st) {
+                              const float *sink, const StackAttn &c, const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb,
+                              int bq, const int *page_table, int max_pages, int page_size, void *out, long long ld_out, int out_off,
+                              float out_scale, const float *vrot, const float *gate, long long ld_gate, int n_split,
+                              int keys_per_split, float *part, cudaStream_t st) {
   if (n_qb <= 0) return cudaSuccess;
+  if (!(c.flags & DIS_ATTN_SINK)) sink = nullptr;
+  if (!(c.flags & DIS_ATTN_GATE)) gate = nullptr;
   if (n_split <= 1 || !part) { n_split = 1; part = nullptr; }
   if (n_split > kAtMaxSplit) return cudaErrorInvalidValue;
   const bool sig = (c.flags & DIS_ATTN_SIGMOID) != 0;
@@ -568,7 +610,7 @@ cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vp
     if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_attn_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
   }));
-  const AttnOut o{out, ld_out, out_off, out_scale, (c.flags & DIS_ATTN_ROT_V) ? vrot : nullptr};
+  const AttnOut o{out, ld_out, out_off, out_scale, (c.flags & DIS_ATTN_ROT_V) ? vrot : nullptr, gate, ld_gate};
   const dim3 grid(n_qb, c.G, n_split);
   static int use_mma = -1;
   if (use_mma < 0) { const char *e = getenv("DIS_STACK_ATTN_MMA"); use_mma = (e && atoi(e) == 0) ? 0 : 1; }
@@ -585,7 +627,7 @@ cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vp
     const size_t shm = (size_t)4 * kMmKeys * ((small ? 64 : 128) + 8) * sizeof(uint16_t);
     const uint16_t *kp = reinterpret_cast<const uint16_t *>(kpool), *vp = reinterpret_cast<const uint16_t *>(vpool);
 #define DIS_ATTN_MMA(D, S) \
-  stack_attn_mma_kernel<D, S><<<grid, kMmWarps * 32, shm, st>>>(qf, kp, vp, temp, pb, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, o, keys_per_split, part)
+  stack_attn_mma_kernel<D, S><<<grid, kMmWarps * 32, shm, st>>>(qf, kp, vp, temp, pb, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, o, keys_per_split, part)
     if (small && sig) DIS_ATTN_MMA(64, true);
     else if (small) DIS_ATTN_MMA(64, false);
     else if (sig) DIS_ATTN_MMA(128, true);
@@ -600,7 +642,7 @@ cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vp
   }
   const int th = kAtWarps * 32;
 #define DIS_ATTN_LAUNCH(F, S) \
-  stack_attn_kernel<F, S><<<grid, th, sh, st>>>(qf, kpool, vpool, temp, pb, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, o, keys_per_split, part)
+  stack_attn_kernel<F, S><<<grid, th, sh, st>>>(qf, kpool, vpool, temp, pb, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, o, keys_per_split, part)
   if (f32 && sig) DIS_ATTN_LAUNCH(true, true);
   else if (f32) DIS_ATTN_LAUNCH(true, false);
   else if (sig) DIS_ATTN_LAUNCH(false, true);

@@ -146,16 +146,32 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       if ((lc.attn_flags & DIS_ATTN_ROT_V) && (lc.vdim & 1)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "rotated values need an even vdim");
       if (lc.rot_factor != 0.f && (lc.rot_high == lc.rot_low || lc.rot_original <= 0 || lc.rot_low <= 0.f || lc.rot_high <= 0.f))
         return fail(DIS_ERR_INVALID_ARGUMENT, at + "rotary scaling needs original > 0 and 0 < low != high");
+      const unsigned fl = lc.attn_flags;
+      if ((fl & DIS_ATTN_SINK) && (fl & DIS_ATTN_SIGMOID)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "a sink belongs to softmax weights");
+      if ((fl & DIS_ATTN_QK_NORM) && (fl & DIS_ATTN_QK_NORM_HEAD)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "query/key norm: whole projection or per head, not both");
+      if ((fl & DIS_ATTN_BIAS) && (fl & DIS_ATTN_BIAS_QKV)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "biases: q, k, o or q, k, v, not both");
+      if (lc.mask_chunk < 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "mask_chunk must not be negative");
+      if (lc.kv_from >= 0) {
+        if (lc.kv_from >= i) return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_from must name an earlier layer");
+        const dis_layer_config &src = M.layers[(size_t)lc.kv_from].c;
+        if ((src.mixer != DIS_MIX_ATTENTION && src.mixer != DIS_MIX_PARALLEL) || src.kv_from >= 0 || src.kv_heads != lc.kv_heads ||
+            src.dim != lc.dim || src.vdim != lc.vdim || src.rot_dims != lc.rot_dims || src.rot_base != lc.rot_base ||
+            ((src.attn_flags ^ fl) & DIS_ATTN_ROT_V))
+          return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_from must name an attention layer with a cache of its own and the same kv_heads, dim, vdim and rotation");
+      }
       const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
-      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, sc->norm_eps};
+      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, sc->norm_eps, lc.mask_chunk};
       const int bq = stack_attn_block_tokens(sa, sc->compute_dtype == DIS_F32);
       if (((size_t)32 * (d + dv + 10) + (size_t)(H / G) * (d + dv + 2)) * 4 > 200 * 1024) return fail(DIS_ERR_INVALID_ARGUMENT, at + "dim + vdim does not fit shared memory");
       stack_abq = stack_abq ? std::min(stack_abq, bq) : bq;
       stack_att_heads = std::max(stack_att_heads, H);
       stack_att_groups = stack_att_groups ? std::min(stack_att_groups, G) : G;
       stack_att_rec = std::max(stack_att_rec, (size_t)H * (dv + 2));
+      // rows of the input projection: q | k | v (a layer with a cache of its own) | one gate row per head
       L.q_off = 0; L.k_off = H * d; L.v_off = L.k_off + G * d;
-      L.n_in = L.v_off + ((lc.attn_flags & DIS_ATTN_V_IS_K) ? 0 : G * dv);
+      L.n_in = lc.kv_from >= 0 ? H * d : L.v_off + ((lc.attn_flags & DIS_ATTN_V_IS_K) ? 0 : G * dv);
+      if (lc.kv_from >= 0) L.k_off = L.v_off = 0;
+      if (fl & DIS_ATTN_GATE) { L.g_off = L.n_in; L.n_in += H; }
       L.n_act = H * dv;
       if (lc.mixer == DIS_MIX_PARALLEL) {
         const int Hr = lc.gla_heads, dr = lc.gla_dim, dvr = lc.gla_vdim;
@@ -168,14 +184,22 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         L.n_act += Hr * dvr;
       }
     } else return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown mixer");
-    if (lc.mlp_act != DIS_ACT_CLAMPED && lc.mlp_act != DIS_ACT_GELU_TANH) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown feed-forward activation");
+    if (lc.mlp_act != DIS_ACT_CLAMPED && lc.mlp_act != DIS_ACT_GELU_TANH && lc.mlp_act != DIS_ACT_SILU) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown feed-forward activation");
     if (lc.mlp == DIS_MLP_DENSE) { if (lc.ff <= 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "ff"); }
     else if (lc.mlp == DIS_MLP_MOE) {
       if (lc.ff <= 0 || lc.experts <= 0 || lc.top <= 0 || lc.top > lc.experts || lc.top > 32 || lc.experts > 1024)
         return fail(DIS_ERR_INVALID_ARGUMENT, at + "experts: 1 <= top <= min(experts, 32), experts <= 1024");
+      if (lc.route_kind != DIS_ROUTE_SOFTMAX_TOP && lc.route_kind != DIS_ROUTE_SIGMOID_GROUPS) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown router kind");
+      if (lc.route_groups > 1) {
+        if (lc.route_kind != DIS_ROUTE_SIGMOID_GROUPS || lc.experts % lc.route_groups || lc.route_keep < 1 || lc.route_keep > lc.route_groups ||
+            lc.route_keep * (lc.experts / lc.route_groups) < lc.top)
+          return fail(DIS_ERR_INVALID_ARGUMENT, at + "expert groups: a divisor of experts, 1 <= keep <= groups, and the kept groups must hold at least top experts");
+      }
+      if (lc.shared_ff < 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "shared_ff");
     } else if (lc.mlp != DIS_MLP_NONE) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown feed-forward kind");
   }
-  if (sc->norm_kind != DIS_NORM_RMS_SCALAR && sc->norm_kind != DIS_NORM_LAYER) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: norm_kind");
+  if (sc->norm_kind != DIS_NORM_RMS_SCALAR && sc->norm_kind != DIS_NORM_LAYER && sc->norm_kind != DIS_NORM_RMS) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: norm_kind");
+  if (sc->logit_softcap < 0.f) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: logit_softcap must not be negative");
   if (sc->loop_times < 0 || (sc->loop_times > 0 && !(0 <= sc->loop_start && sc->loop_start < sc->loop_stop && sc->loop_stop <= sc->n_layers)))
     return fail(DIS_ERR_INVALID_ARGUMENT, "stack: a loop needs 0 <= loop_start < loop_stop <= n_layers");
   if (M.c.embed_scale == 0.f) M.c.embed_scale = 1.f;
@@ -191,9 +215,9 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     StackRun r; r.layer = i;
     M.runs.push_back(r);
   }
-  for (size_t ri = 0; ri < M.runs.size(); ri++) {  // a latent layer that borrows a cache reads the latest run of its owner
+  for (size_t ri = 0; ri < M.runs.size(); ri++) {  // a layer that borrows a cache reads the latest run of its owner
     const StackLayer &L = M.layers[(size_t)M.runs[ri].layer];
-    if (L.c.mixer != DIS_MIX_LATENT) continue;
+    if (L.c.mixer != DIS_MIX_LATENT && L.c.mixer != DIS_MIX_ATTENTION && L.c.mixer != DIS_MIX_PARALLEL) continue;
     M.runs[ri].kv_run = (int)ri;
     if (L.c.kv_from >= 0)
       for (size_t rj = 0; rj < ri; rj++) if (M.runs[rj].layer == L.c.kv_from) M.runs[ri].kv_run = (int)rj;
@@ -234,12 +258,15 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   name("embed", &M.embed, 0, {sc->vocab, W}, -1);
   name("head", &M.head, 0, {sc->vocab, W}, -1);
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.final_g), 4));
-  const bool ln = sc->norm_kind == DIS_NORM_LAYER;
+  const bool ln = sc->norm_kind == DIS_NORM_LAYER || sc->norm_kind == DIS_NORM_RMS;  // norms with vectors
+  const bool ln_bias = sc->norm_kind == DIS_NORM_LAYER;
   if (ln) {
     ENG_CUDA(tensor(M.final_w, (size_t)W, true));
-    ENG_CUDA(tensor(M.final_b, (size_t)W, true));
     name("final.norm", &M.final_w, 0, {W}, -1);
-    name("final.norm.b", &M.final_b, 0, {W}, -1);
+    if (ln_bias) {
+      ENG_CUDA(tensor(M.final_b, (size_t)W, true));
+      name("final.norm.b", &M.final_b, 0, {W}, -1);
+    }
   }
   if (sc->loop_times > 0) {
     ENG_CUDA(tensor(M.loop_in, (size_t)W * 2 * W, M.f32));
@@ -251,6 +278,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   (void)dummy;
   size_t max_proj = 1, max_mix = 1, max_act = 1, max_qf = 1, max_vrot = 0, max_dec = 0;
   int max_top = 0, max_e = 0;
+  bool any_shared = false;
   const size_t slots = (size_t)max_batch;
   std::vector<StackTensor *> scalars;
   for (int i = 0; i < sc->n_layers; i++) {
@@ -267,8 +295,9 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       for (int k = 0; k < 4; k++) {
         if (k >= 2 && lc.mlp == DIS_MLP_NONE) continue;
         ENG_CUDA(tensor(L.ln_w[k], (size_t)W, true));
-        ENG_CUDA(tensor(L.ln_b[k], (size_t)W, true));
         name(pre + gn[k], &L.ln_w[k], 0, {W}, i);
+        if (!ln_bias) continue;
+        ENG_CUDA(tensor(L.ln_b[k], (size_t)W, true));
         name(pre + gn[k] + ".b", &L.ln_b[k], 0, {W}, i);
       }
     }
@@ -291,9 +320,11 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     } else if (lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) {
       const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
       const std::string a = pre + (lc.mixer == DIS_MIX_PARALLEL ? "mix.left." : "mix.");
+      const bool own = lc.kv_from < 0;
       name(a + "q", &L.w_in, 0, {H * d, W}, i);
-      name(a + "k", &L.w_in, (size_t)L.k_off * W, {G * d, W}, i);
-      if (!(lc.attn_flags & DIS_ATTN_V_IS_K)) name(a + "v", &L.w_in, (size_t)L.v_off * W, {G * dv, W}, i);
+      if (own) name(a + "k", &L.w_in, (size_t)L.k_off * W, {G * d, W}, i);
+      if (own && !(lc.attn_flags & DIS_ATTN_V_IS_K)) name(a + "v", &L.w_in, (size_t)L.v_off * W, {G * dv, W}, i);
+      if (lc.attn_flags & DIS_ATTN_GATE) name(a + "g", &L.w_in, (size_t)L.g_off * W, {H, W}, i);
       ENG_CUDA(tensor(L.w_o, (size_t)W * L.n_act, M.f32));
       {
         name(a + "o", &L.w_o, 0, {W, H * dv}, i, 2);
@@ -305,6 +336,23 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         name(a + "k.b", &L.b_in, (size_t)L.k_off, {G * d}, i);
         ENG_CUDA(tensor(L.b_o, (size_t)W, true));
         name(a + "o.b", &L.b_o, 0, {W}, i);
+      }
+      if (lc.attn_flags & DIS_ATTN_BIAS_QKV) {
+        ENG_CUDA(tensor(L.b_in, (size_t)L.n_in, true));
+        name(a + "q.b", &L.b_in, 0, {H * d}, i);
+        if (own) {
+          name(a + "k.b", &L.b_in, (size_t)L.k_off, {G * d}, i);
+          name(a + "v.b", &L.b_in, (size_t)L.v_off, {G * dv}, i);
+        }
+      }
+      if (lc.attn_flags & DIS_ATTN_QK_NORM_HEAD) {
+        ENG_CUDA(tensor(L.qk_norm, (size_t)2 * d, true));
+        name(a + "q.norm", &L.qk_norm, 0, {d}, i);
+        if (own) name(a + "k.norm", &L.qk_norm, (size_t)d, {d}, i);
+      }
+      if (lc.attn_flags & DIS_ATTN_SINK) {
+        ENG_CUDA(tensor(L.sink, (size_t)H, true));
+        name(a + "sink", &L.sink, 0, {H}, i);
       }
       if (lc.attn_flags & DIS_ATTN_QK_NORM) {
         ENG_CUDA(tensor(L.qk_norm, (size_t)(H + G) * d, true));
@@ -415,8 +463,24 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       const int ff = lc.ff, E = lc.experts;
       ENG_CUDA(tensor(L.w_gu, (size_t)E * 2 * ff * W, M.f32));
       ENG_CUDA(tensor(L.w_down, (size_t)E * W * ff, M.f32));
-      ENG_CUDA(tensor(L.router, (size_t)E * W, true));
+      ENG_CUDA(tensor(L.router, (size_t)(E + (lc.shared_ff > 0 ? 1 : 0)) * W, true));
       name(pre + "mlp.router", &L.router, 0, {E, W}, i);
+      if (lc.route_kind == DIS_ROUTE_SIGMOID_GROUPS) {
+        ENG_CUDA(tensor(L.correction, (size_t)E, true));
+        name(pre + "mlp.correction", &L.correction, 0, {E}, i);
+      }
+      if (lc.shared_ff > 0) {  // the shared expert: a dense unit of its own size; the logit of its gate is one more router row
+        const int sf = lc.shared_ff;
+        ENG_CUDA(tensor(L.w_sgu, (size_t)2 * sf * W, M.f32));
+        ENG_CUDA(tensor(L.w_sdown, (size_t)W * sf, M.f32));
+        name(pre + "mlp.shared.gate", &L.w_sgu, 0, {sf, W}, i);
+        name(pre + "mlp.shared.up", &L.w_sgu, (size_t)sf * W, {sf, W}, i);
+        name(pre + "mlp.shared.down", &L.w_sdown, 0, {W, sf}, i);
+        name(pre + "mlp.shared.sg", &L.router, (size_t)E * W, {1, W}, i);
+        max_proj = std::max(max_proj, (size_t)2 * sf);
+        max_act = std::max(max_act, (size_t)sf);
+        any_shared = true;
+      }
       for (int e = 0; e < E; e++) {
         const std::string ep = pre + "mlp.e" + std::to_string(e) + ".";
         name(ep + "gate", &L.w_gu, (size_t)e * 2 * ff * W, {ff, W}, i);
@@ -552,6 +616,10 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.where), rows * 4));
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.tiles), (size_t)(1 + 3 * M.max_tiles) * 4));
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.rows_out), rows * W * 4));
+    if (any_shared) {
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&M.y2), cap * W * 4));
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&M.r_sg), cap * 4));
+    }
     if (!M.f32 && stack_tc) {
       ENG_CUDA(alloc(&M.moe_x, rows * W * 2));
       ENG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&M.h_counts), (size_t)max_e * sizeof(int)));
@@ -561,13 +629,14 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   ENG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&M.h_out), (size_t)2 * M.max_rows * 4));
   ENG_CUDA(stack_meta(meta_pre, cap_tokens, M.max_rows));
   cur_meta = &meta_pre;
-  // ---- pages: one pool per latent layer that owns a cache, rows of kv_rank + rot_dim elements; a page id is valid in all
+  // ---- pages: one pool per latent layer that owns a cache (rows of kv_rank + rot_dim elements), a key and a value pool per
+  // attention layer that owns one; a page id is valid in all
   {
     size_t row_bytes = 0;
     for (auto &R : M.runs) {
       const dis_layer_config &lc = M.layers[(size_t)R.layer].c;
       if (lc.mixer == DIS_MIX_LATENT && lc.kv_from < 0) row_bytes += (size_t)(lc.kv_rank + lc.rot_dim) * esz;
-      if (lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) row_bytes += (size_t)lc.kv_heads * (lc.dim + lc.vdim) * esz;
+      if ((lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) && lc.kv_from < 0) row_bytes += (size_t)lc.kv_heads * (lc.dim + lc.vdim) * esz;
     }
     int64_t want = c->kv_pages;
     const int64_t useful = (int64_t)max_batch * max_pages;
@@ -584,7 +653,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       const dis_layer_config &lc = M.layers[(size_t)R.layer].c;
       if (lc.mixer == DIS_MIX_LATENT && lc.kv_from < 0)
         ENG_CUDA(alloc(&R.pool, (size_t)n_pages * page_size * (lc.kv_rank + lc.rot_dim) * esz));
-      if (lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) {
+      if ((lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) && lc.kv_from < 0) {
         ENG_CUDA(alloc(&R.kpool, (size_t)n_pages * page_size * lc.kv_heads * lc.dim * esz));
         ENG_CUDA(alloc(&R.vpool, (size_t)n_pages * page_size * lc.kv_heads * lc.vdim * esz));
       }
@@ -789,15 +858,26 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
     sp = (stack_max_ctx + keys - 1) / keys;
     if (sp > 1 && (size_t)sp * T * stack_lat_rec <= M.lat_part_elems) { stack_lat_split = sp; stack_lat_keys = keys; }
   }
-  // paged attention likewise: one CTA per (query block, key/value head, slice)
+  // paged attention likewise: one CTA per (query block, key/value head, slice).  A layer with a chunked mask walks at most
+  // its chunk (plus the block's own tokens) whatever the history's length, so it slices by that bound.
   stack_kb = KB;
-  stack_att_split = 1; stack_att_keys = 0;
-  if (KB > 0 && KB * stack_att_groups < kNumSMs && stack_max_ctx >= 256 && stack_att_rec) {
-    int sp = std::min(std::min((2 * kNumSMs + KB * stack_att_groups - 1) / (KB * stack_att_groups), stack_max_ctx / 64), 64);
-    if (sp > 1) {
-      const int keys = ((stack_max_ctx + sp - 1) / sp + 31) / 32 * 32;
-      sp = (stack_max_ctx + keys - 1) / keys;
-      if (sp > 1 && (size_t)sp * T * stack_att_rec <= M.attn_part_elems) { stack_att_split = sp; stack_att_keys = keys; }
+  auto att_slices = [&](int ctx) -> std::pair<int, int> {
+    if (!(KB > 0 && KB * stack_att_groups < kNumSMs && ctx >= 256 && stack_att_rec)) return {1, 0};
+    int sp = std::min(std::min((2 * kNumSMs + KB * stack_att_groups - 1) / (KB * stack_att_groups), ctx / 64), 64);
+    if (sp <= 1) return {1, 0};
+    const int keys = ((ctx + sp - 1) / sp + 31) / 32 * 32;
+    sp = (ctx + keys - 1) / keys;
+    if (sp > 1 && (size_t)sp * T * stack_att_rec <= M.attn_part_elems) return {sp, keys};
+    return {1, 0};
+  };
+  {
+    const std::pair<int, int> whole = att_slices(stack_max_ctx);
+    stack_att_split = whole.first; stack_att_keys = whole.second;
+    stack_att_plan.assign(M.layers.size(), whole);
+    for (size_t li = 0; li < M.layers.size(); li++) {
+      const dis_layer_config &lc = M.layers[li].c;
+      if ((lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) && lc.mask_chunk > 0)
+        stack_att_plan[li] = att_slices((int)std::min<long long>(stack_max_ctx, (long long)lc.mask_chunk + stack_abq));
     }
   }
   // A pass of single tokens only (decode rows, no kept prompt positions) has the same launches whenever its size, its
@@ -806,8 +886,10 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
   if (!graphable) {
     ENG_CUDA(stack_forward(T, SP, QB, R, all_greedy));
   } else {
-    const uint64_t key = (uint64_t)T | ((uint64_t)stack_lat_split << 16) | ((uint64_t)(stack_lat_keys / 32) << 24) |
-                         ((uint64_t)stack_att_split << 36) | ((uint64_t)(stack_att_keys / 32) << 43) | (all_greedy ? 1ull << 60 : 0ull);
+    // the pass's shape and every layer's slicing name the graph; `graphs` is keyed by the order in which they were first seen
+    std::vector<uint64_t> shape{(uint64_t)T | ((uint64_t)stack_lat_split << 16) | ((uint64_t)(stack_lat_keys / 32) << 24) | (all_greedy ? 1ull << 60 : 0ull)};
+    for (auto &pl : stack_att_plan) shape.push_back((uint64_t)pl.first | ((uint64_t)pl.second << 8));
+    const uint64_t key = stack_graph_ids.emplace(shape, (uint64_t)stack_graph_ids.size()).first->second;
     auto it = graphs.find(key);
     if (it != graphs.end() && it->second) {
       ENG_CUDA(cudaGraphLaunch(it->second, stream));
@@ -815,7 +897,7 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
     } else if (it == graphs.end()) {
       if (graphs.size() > 256) {  // histories that grow through many slicings: start over rather than keep every graph
         for (auto &g : graphs) if (g.second) cudaGraphExecDestroy(g.second);
-        graphs.clear();
+        graphs.clear();  // (the ids stay: an id names one shape for the engine's life)
       }
       const uint64_t before = kernel_launches;
       ENG_CUDA(stack_forward(T, SP, QB, R, all_greedy));  // first sight: plain launches (function attributes, tensor maps)
@@ -937,7 +1019,8 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   };
   RET_CUDA(launch_stack_embed(M.embed.ptr, f32, sp.tokens, M.x, M.x0, M.c.embed_scale, T, W, stream)); kl++;
   const float *pend_y = nullptr, *pend_post = nullptr, *pend_post_b = nullptr;
-  const bool ln = M.c.norm_kind == DIS_NORM_LAYER;
+  const bool ln = M.c.norm_kind == DIS_NORM_LAYER || M.c.norm_kind == DIS_NORM_RMS;  // norms with vectors: one boundary kernel
+  const bool rms = M.c.norm_kind == DIS_NORM_RMS;
   const bool single = T == n_spans;  // every span one token long: the fused boundary kernel
   // The boundary in front of a sublayer: the product before it joins the residual through its post norm, then the pre norm (and
   // the convolution) makes the sublayer's input.  pre == null: only the residual is updated.  cat: [x ; x0] is written too.
@@ -948,7 +1031,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       const bool conv = pre && taps >= 1;
       const cudaError_t e = launch_stack_boundary_ln(M.x, src, pend_parts, pend_stride, pend_bias, pend_post, pend_post_b, pre, pre_b,
                                                      conv ? M.hn : nullptr, conv ? nullptr : M.hc, M.x0, cat ? M.xcat : nullptr, f32, T, W,
-                                                     eps, stream);
+                                                     eps, rms, stream);
       pend_y = nullptr; pend_parts = 1; pend_bias = nullptr;
       if (e != cudaSuccess || !conv) return e;
       kl += taps > 1 ? 2 : 1;
@@ -964,7 +1047,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       pend_y = nullptr;
       kl++;
       return launch_stack_boundary_ln(M.x, nullptr, 1, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, M.x0, M.xcat, f32, T, W,
-                                      eps, stream);
+                                      eps, false, stream);
     }
     if (single) {
       kl++;
@@ -985,6 +1068,42 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   auto norm_b = [&](StackLayer &L, int k) { return ln ? reinterpret_cast<const float *>(L.ln_b[k].ptr) : nullptr; };
   int max_span = 0;
   for (auto &sh : stack_spans_h) max_span = std::max(max_span, sh.len);
+  // A dense gated unit out = W_down act(W_gate h, W_up h) on the sublayer input M.hc.  later: the slices of the down projection
+  // may stay unsummed for the next boundary kernel (out is then M.y, as the caller expects).
+  auto dense_ff = [&](const StackTensor &w_gu, const StackTensor &b_gu, const StackTensor &w_down, const StackTensor &b_down, int ff,
+                      int act_kind, float limit, float *out, bool later_ok) -> cudaError_t {
+    // bf16, a unit without biases (gelu_tanh or SiLU gate), prompt-sized passes: gate and up run as one tensor-core product with
+    // two accumulators whose epilogue writes act(gate) * up (the product the Llama path uses with SiLU).  Decode-sized passes
+    // keep the split-K product below, whose slices the gated unit sums: at these widths a single pass over K leaves each CTA a
+    // long thin loop (measured: 0.337 against 0.320 ms per step of four layers at width 1024).
+    if (stack_tc && !f32 && (act_kind == DIS_ACT_GELU_TANH || act_kind == DIS_ACT_SILU) && !b_gu.ptr && W % 8 == 0 && !w_gu.f32 &&
+        gemm_token_tile(T) >= 128) {
+      const int tc_act = act_kind == DIS_ACT_GELU_TANH ? 1 : 0;
+      if (stack_persist && gemm_use_persist(T, ff, true)) {  // paired gate / up tiles on the persistent kernel
+        const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, 256);
+        const TmaMap *wm = stack_map(w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, 64);
+        if (!xm || !wm) return cudaErrorInvalidValue;
+        RET_CUDA(launch_gemm_persist_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, tc_act, stream));
+      } else {
+        const int tr = 128;
+        const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, (uint32_t)gemm_token_tile(T));
+        const TmaMap *wm = stack_map(w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, (uint32_t)tr);
+        if (!xm || !wm) return cudaErrorInvalidValue;
+        RET_CUDA(launch_gemm_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, tr, tc_act, stream));
+      }
+      kl++;
+      return gemm(M.act, f32, ff, w_down, 0, nullptr, out, T, W, ff, cap_tokens, nullptr, later_ok);
+    }
+    // the gated unit sums the slices of its input product itself and adds the bias the product left out
+    const float *gu_bias = nullptr;
+    RET_CUDA(gemm(M.hc, f32, W, w_gu, 0, reinterpret_cast<const float *>(b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens, &gu_bias, true));
+    const bool sliced = pend_parts > 1 || pend_bias;
+    RET_CUDA(launch_stack_glu(sliced ? pend_src : M.proj, sliced ? pend_parts : 1, pend_stride, sliced ? pend_bias : gu_bias, M.act, f32, nullptr,
+                              T, ff, limit, act_kind, stream));
+    kl++;
+    pend_parts = 1; pend_bias = nullptr;
+    return gemm(M.act, f32, ff, w_down, 0, reinterpret_cast<const float *>(b_down.ptr), out, T, W, ff, cap_tokens, nullptr, later_ok);
+  };
   for (size_t ri = 0; ri < M.runs.size(); ri++) {
     StackRun &Rn = M.runs[ri];
     StackLayer &L = M.layers[(size_t)Rn.layer];
@@ -1023,14 +1142,20 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     } else if (is_attn) {
       const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
       const bool par = lc.mixer == DIS_MIX_PARALLEL;
-      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, eps};
+      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, eps, lc.mask_chunk};
       const float *qkn = reinterpret_cast<const float *>(L.qk_norm.ptr), *tpb = reinterpret_cast<const float *>(L.temp_pb.ptr);
-      RET_CUDA(launch_stack_attn_prep(M.proj, N, L.q_off, L.k_off, L.v_off, in_bias, qkn, qkn ? qkn + (size_t)H * d : nullptr, L.freq, L.vfreq, sa,
-                                      sp, M.qf, Rn.kpool, Rn.vpool, M.vrot, f32, d_page_table, max_pages, page_size, stream));
-      RET_CUDA(launch_stack_attn(M.qf, Rn.kpool, Rn.vpool, f32, tpb, tpb ? tpb + H : nullptr, sa, sp, mt.d<int>(mt.o_kb_tok0),
-                                 mt.d<int>(mt.o_kb_len), stack_kb, single ? 1 : stack_abq, d_page_table, max_pages, page_size, M.act, L.n_act, 0,
-                                 par ? lc.mix_scale : 1.f, M.vrot, stack_att_split, stack_att_keys, M.attn_part, stream));
-      kl += stack_att_split > 1 ? 3 : 2;
+      // the gains of the key norm follow those of the query norm: [H*d] then [G*d] (whole projection), or [d] then [d] (per head)
+      const float *kn = qkn ? qkn + ((lc.attn_flags & DIS_ATTN_QK_NORM_HEAD) ? (size_t)d : (size_t)H * d) : nullptr;
+      const bool own = lc.kv_from < 0;  // else: the keys and values of the layer named by kv_from, as its latest run cached them
+      StackRun &KV = M.runs[(size_t)Rn.kv_run];
+      RET_CUDA(launch_stack_attn_prep(M.proj, N, L.q_off, L.k_off, L.v_off, in_bias, qkn, kn, L.freq, L.vfreq, sa, sp, M.qf,
+                                      own ? Rn.kpool : nullptr, own ? Rn.vpool : nullptr, M.vrot, f32, d_page_table, max_pages, page_size, stream));
+      const std::pair<int, int> slices = stack_att_plan[(size_t)Rn.layer];
+      RET_CUDA(launch_stack_attn(M.qf, KV.kpool, KV.vpool, f32, tpb, tpb ? tpb + H : nullptr, reinterpret_cast<const float *>(L.sink.ptr), sa, sp,
+                                 mt.d<int>(mt.o_kb_tok0), mt.d<int>(mt.o_kb_len), stack_kb, single ? 1 : stack_abq, d_page_table, max_pages,
+                                 page_size, M.act, L.n_act, 0, par ? lc.mix_scale : 1.f, M.vrot, M.proj + L.g_off, N, slices.first,
+                                 slices.second, M.attn_part, stream));
+      kl += slices.first > 1 ? 3 : 2;
       if (par) {
         const int Hr = lc.gla_heads, dr = lc.gla_dim, dvr = lc.gla_vdim;
         RET_CUDA(launch_stack_gla_decay(M.proj, N, L.ga_off, L.a2.ptr, L.a2.f32, reinterpret_cast<const float *>(L.a2_b.ptr), T, Hr * dr,
@@ -1133,41 +1258,16 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     if (lc.mlp == DIS_MLP_NONE) continue;
     RET_CUDA(sublayer_in(norm_w(L, 2), norm_b(L, 2), L.canon2, Rn.cstate2));
     if (lc.mlp == DIS_MLP_DENSE) {
-      const int ff = lc.ff;
-      // bf16, gelu unit without biases, prompt-sized passes: gate and up run as one tensor-core product with two accumulators
-      // whose epilogue writes gelu_tanh(gate) * up (the product the Llama path uses with SiLU).  Decode-sized passes keep the
-      // split-K product below, whose slices the gated unit sums: at these widths a single pass over K leaves each CTA a
-      // long thin loop (measured: 0.337 against 0.320 ms per step of four layers at width 1024).
-      if (stack_tc && !f32 && lc.mlp_act == DIS_ACT_GELU_TANH && !L.b_gu.ptr && W % 8 == 0 && !L.w_gu.f32 && gemm_token_tile(T) >= 128) {
-        if (stack_persist && gemm_use_persist(T, ff, true)) {  // paired gate / up tiles on the persistent kernel
-          const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, 256);
-          const TmaMap *wm = stack_map(L.w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, 64);
-          if (!xm || !wm) return cudaErrorInvalidValue;
-          RET_CUDA(launch_gemm_persist_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, 1, stream));
-        } else {
-          const int tr = 128;
-          const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, (uint32_t)gemm_token_tile(T));
-          const TmaMap *wm = stack_map(L.w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, (uint32_t)tr);
-          if (!xm || !wm) return cudaErrorInvalidValue;
-          RET_CUDA(launch_gemm_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, tr, 1, stream));
-        }
-        kl++;
-        RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, nullptr, M.y, T, W, ff, cap_tokens, nullptr, later));
-        pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
-        continue;
-      }
-      // the gated unit sums the slices of its input product itself and adds the bias the product left out
-      const float *gu_bias = nullptr;
-      RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens, &gu_bias, true));
-      const bool sliced = pend_parts > 1 || pend_bias;
-      RET_CUDA(launch_stack_glu(sliced ? pend_src : M.proj, sliced ? pend_parts : 1, pend_stride, sliced ? pend_bias : gu_bias, M.act, f32, nullptr,
-                                T, ff, lc.limit, lc.mlp_act, stream));
-      kl++;
-      pend_parts = 1; pend_bias = nullptr;
-      RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff, cap_tokens, nullptr, later));
+      RET_CUDA(dense_ff(L.w_gu, L.b_gu, L.w_down, L.b_down, lc.ff, lc.mlp_act, lc.limit, M.y, later));
     } else {
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
-      RET_CUDA(launch_stack_route(M.hc, f32, reinterpret_cast<const float *>(L.router.ptr), T, W, E, top, M.r_idx, M.r_wt, stream));
+      // the always-on unit beside the experts: its dense unit first (it borrows the buffers the experts' rows use afterwards);
+      // the logit of its per-token gate is one more row of the router matrix, and the combine kernel adds it in
+      const bool shared = lc.shared_ff > 0;
+      if (shared) RET_CUDA(dense_ff(L.w_sgu, StackTensor(), L.w_sdown, StackTensor(), lc.shared_ff, lc.mlp_act, lc.limit, M.y2, false));
+      const float *router = reinterpret_cast<const float *>(L.router.ptr);
+      RET_CUDA(launch_stack_route(M.hc, f32, router, T, W, E, top, lc.route_kind, reinterpret_cast<const float *>(L.correction.ptr), lc.route_groups,
+                                  lc.route_keep, shared ? router + (size_t)E * W : nullptr, M.r_sg, M.r_idx, M.r_wt, stream));
       RET_CUDA(launch_stack_moe_plan(M.r_idx, T, top, E, kStackGemmTile, M.counts, M.perm_tok, M.where, M.tiles, M.max_tiles, stream));
       // Large passes in bf16: one tensor-core product per expert over its rows.  The row counts come back to the host (one
       // small copy and a wait), so this path is not taken while a decode pass is being captured into a graph.
@@ -1199,7 +1299,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
           RET_CUDA(launch_gemm_partial(*wm, xm, M.rows_out + (size_t)off * W, cnt, W, ff, 0, 1, stream));
           off += cnt; kl++;
         }
-        RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, M.y, T, W, top, stream));
+        RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? M.y2 : nullptr, M.r_sg, M.y, T, W, top, stream));
         pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
         continue;
       }
@@ -1217,7 +1317,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       dn.out = M.rows_out; dn.ldo = W; dn.M = rows; dn.N = W; dn.K = ff;
       dn.tiles = M.tiles; dn.max_tiles = tiles_cap;
       RET_CUDA(launch_stack_gemm(dn, stream));
-      RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, M.y, T, W, top, stream));
+      RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? M.y2 : nullptr, M.r_sg, M.y, T, W, top, stream));
       kl += 6;
     }
     pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
@@ -1227,11 +1327,13 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   else { RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++; }
   if (R <= 0) return cudaSuccess;
   if (ln) RET_CUDA(launch_stack_final_ln(M.x, mt.d<int>(mt.o_rowmap), reinterpret_cast<const float *>(M.final_w.ptr),
-                                         reinterpret_cast<const float *>(M.final_b.ptr), M.xr, f32, R, W, eps, M.c.logit_scale, stream));
+                                         rms ? nullptr : reinterpret_cast<const float *>(M.final_b.ptr), M.xr, f32, R, W, eps, M.c.logit_scale,
+                                         stream));
   else RET_CUDA(launch_stack_final_norm(M.x, mt.d<int>(mt.o_rowmap), M.final_g, M.xr, f32, R, W, eps, stream));
   kl++;
   RET_CUDA(gemm(M.xr, f32, W, M.head, 0, nullptr, M.logits, R, M.c.vocab, W, M.max_rows));
   if (!ln && M.c.logit_scale != 1.f) { RET_CUDA(launch_stack_scale(M.logits, (long long)R * M.c.vocab, M.c.logit_scale, stream)); kl++; }
+  if (M.c.logit_softcap > 0.f) { RET_CUDA(launch_stack_softcap(M.logits, (long long)R * M.c.vocab, M.c.logit_softcap, stream)); kl++; }
   const float *temp = mt.d<float>(mt.o_temp), *topp = mt.d<float>(mt.o_topp);
   const unsigned long long *seed = mt.d<unsigned long long>(mt.o_seed), *step = mt.d<unsigned long long>(mt.o_step);
   float *d_logprob = reinterpret_cast<float *>(M.d_out + M.max_rows);

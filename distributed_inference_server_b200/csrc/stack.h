@@ -62,11 +62,15 @@ cudaError_t launch_stack_boundary_single(float *x, const float *y, int n_part, l
 // (compute type, when given).  post / pre null: that step is left out.
 cudaError_t launch_stack_boundary_ln(float *x, const float *y, int n_part, long long stride, const float *bias, const float *post_w,
                                      const float *post_b, const float *pre_w, const float *pre_b, float *hn, void *hc, const float *x0,
-                                     void *cat, bool f32, int T, int W, float eps, cudaStream_t st);
-// out = LN(x[row_map[r]]) * scale: a factor on the logits is applied to the head's input (head (s v) = s (head v))
+                                     void *cat, bool f32, int T, int W, float eps, bool rms, cudaStream_t st);
+// rms: both norms are v / sqrt(mean(v^2) + eps) * w (gain vectors, no mean taken off, no bias vectors)
+// out = LN(x[row_map[r]]) * scale: a factor on the logits is applied to the head's input (head (s v) = s (head v)).
+// b == null: the RMS form with the gain vector w
 cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const float *w, const float *b, void *out, bool f32, int R, int W,
                                   float eps, float scale, cudaStream_t st);
 cudaError_t launch_stack_scale(float *v, long long n, float s, cudaStream_t st);
+// v = cap * tanh(v / cap)
+cudaError_t launch_stack_softcap(float *v, long long n, float cap, cudaStream_t st);
 cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long n, cudaStream_t st);
 // proj [T][ld]: q at 0, k at H*d, v at 2*H*d (pre-activation).  state [slots][H][d][dv].  o [T][H*dv] fp32.
 // seg (or null): room for stack_lightning_seg_floats() floats -- spans longer than stack_lightning_seg_tokens() (max_len: the
@@ -93,11 +97,14 @@ struct StackAttn {
   int H, G, d, dv, rot_dims;
   unsigned flags;  // DIS_ATTN_*
   float scale, eps;
+  int chunk;       // > 0: position i sees only keys from floor(i / chunk) * chunk on
 };
-// Per token: (bias), query/key norm over the whole projection, rotation of the first rot_dims coordinates of every head by
+// Per token: (bias, one entry per column of proj), query/key norm over the whole projection (gains qn [H*d], kn [G*d]) or per
+// head (DIS_ATTN_QK_NORM_HEAD: gains [d] shared by the heads), rotation of the first rot_dims coordinates of every head by
 // pos * freq[i] (pairs i, i + rot_dims/2); queries to qf [T][H*d]; rotated keys and the values (own projection at v_off, or the
 // unrotated keys; rotated by pos * vfreq[m] over pairs m, m + dv/2 with DIS_ATTN_ROT_V) to the token's row of the pools
 // ([pages*page_size][G*d] and [..][G*dv]); vrot [T][dv] receives cos | sin of the value angles for the output's rotation back.
+// kpool == null: the layer reads another layer's cache -- only the queries are prepared.
 cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, int k_off, int v_off, const float *bias, const float *qn,
                                    const float *kn, const double *freq, const double *vfreq, const StackAttn &c, const StackSpans &sp,
                                    float *qf, void *kpool, void *vpool, float *vrot, bool f32, const int *page_table, int max_pages,
@@ -106,12 +113,16 @@ cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, i
 // of 32), records of dv + 2 floats per (slice, token, head) in `part`, merged by a second kernel.  The result, times out_scale
 // and rotated back when values were rotated, lands in out [T][ld_out] (compute type) at columns out_off + h * dv.
 // bf16 with dim % 8 == 0, vdim % 16 == 0, both <= 128 and at most 64 query heads per key/value head: the mma.sync kernel (blocks
-// of 64 (token, head) rows); otherwise the fp32-arithmetic kernel
+// of 64 (token, head) rows); otherwise the fp32-arithmetic kernel.
+// sink [H] (DIS_ATTN_SINK): per-head logit in the softmax denominator.  gate [T][ld_gate] (DIS_ATTN_GATE): head h's output is
+// multiplied by sigmoid(gate[t][h]).  With c.chunk > 0 a block's history starts at the chunk of its first token, and the slices
+// are counted from there.
 int stack_attn_block_tokens(const StackAttn &c, bool f32);
 cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vpool, bool f32, const float *temp, const float *pb,
-                              const StackAttn &c, const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb, int bq,
-                              const int *page_table, int max_pages, int page_size, void *out, long long ld_out, int out_off,
-                              float out_scale, const float *vrot, int n_split, int keys_per_split, float *part, cudaStream_t st);
+                              const float *sink, const StackAttn &c, const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb,
+                              int bq, const int *page_table, int max_pages, int page_size, void *out, long long ld_out, int out_off,
+                              float out_scale, const float *vrot, const float *gate, long long ld_gate, int n_split,
+                              int keys_per_split, float *part, cudaStream_t st);
 // out = unit_rms(o) * w * sigmoid(gate) per token over n = H*dv coordinates; gate [T][ldg]
 cudaError_t launch_stack_norm_gate(const float *o, const float *w, const float *gate, long long ldg, void *out, bool f32, int T,
                                    int n, float eps, cudaStream_t st);
@@ -154,21 +165,27 @@ cudaError_t launch_stack_latent_gather(const void *pool, const int *pt_row, int 
 cudaError_t launch_stack_latent_softmax(const float *S, int rows, int ld, const float *sink, int H, int pos_first, float scale,
                                         uint16_t *P, cudaStream_t st);
 // kind DIS_ACT_CLAMPED: act = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit);
-// DIS_ACT_GELU_TANH: act = gelu_tanh(g) u.  gu [M][2*ff] (gate | up)
+// DIS_ACT_GELU_TANH: act = gelu_tanh(g) u; DIS_ACT_SILU: act = g sigmoid(g) u.  gu [M][2*ff] (gate | up)
 // gu may come as n_part split-K slices (slice stride `stride`), summed here; bias (or null): [2*ff], added here when the product
 // that made gu left it out
 cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, const float *bias, void *act, bool f32, const int *rows_ptr,
                              int M, int ff, float limit, int kind, cudaStream_t st);
-// Router: logits in fp32 from hc and the fp32 router matrix; top-k by value (lowest index wins a tie); softmax over the chosen.
-cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int *idx, float *wt,
+// Router: logits in fp32 from hc and the fp32 router matrix; `top` experts by value (lowest index wins a tie).
+// kind DIS_ROUTE_SOFTMAX_TOP: by logit, weights = softmax over the chosen.  DIS_ROUTE_SIGMOID_GROUPS: by sigmoid(logit) +
+// correction[e] among the experts of the `keep` best of `groups` contiguous runs (a run ranks by the sum of its top two
+// choice scores; groups <= 1: all experts), weights = the chosen sigmoids over their sum (+ 1e-20).
+// extra (or null): one more fp32 row [W]; its product with every token goes to extra_out [T].
+cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int kind,
+                               const float *correction, int groups, int keep, const float *extra, float *extra_out, int *idx, float *wt,
                                cudaStream_t st);
 // Row plan of the experts: counts / cursor [E] ints (zeroed inside), perm_tok [T*top], where [T*top] (row of (t, k)),
 // tiles [1 + 3 * max_tiles], rows_total[1]
 cudaError_t launch_stack_moe_plan(const int *idx, int T, int top, int E, int tile_rows, int *counts, int *perm_tok, int *where,
                                   int *tiles, int max_tiles, cudaStream_t st);
 cudaError_t launch_stack_moe_gather(const void *hc, const int *perm_tok, void *xs, int rows, int W, cudaStream_t st);
-cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, float *y, int T, int W, int top,
-                                     cudaStream_t st);
+// y[t] = sum_k wt[t][k] * rows[where[t][k]] (+ sigmoid(shared_gate[t]) * shared[t] when shared is given)
+cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, const float *shared,
+                                     const float *shared_gate, float *y, int T, int W, int top, cudaStream_t st);
 cudaError_t launch_stack_final_norm(const float *x, const int *row_map, const float *g, void *out, bool f32, int R, int W, float eps,
                                     cudaStream_t st);
 // out[m][n] = bias[n] + sum_s part[s][m][n]: the split-K slices of a tensor-core product, with the projection's bias
@@ -195,7 +212,7 @@ struct StackLayer {
   StackTensor norm_w;   // lightning: gain of the head norm; latent: gain of the latent norm (fp32)
   StackTensor ukT;      // latent: per head [r][d] = transpose of the head's block of the key up-projection
   StackTensor uv;       // latent: [H*dv][r]
-  StackTensor sink;     // latent: [H] fp32
+  StackTensor sink;     // latent, attention with DIS_ATTN_SINK: [H] fp32
   StackTensor decay_d;  // lightning: [H] fp32
   int n_in = 0, q_off = 0, dkv_off = 0, g_off = 0;
   float *canon1 = nullptr, *canon2 = nullptr;        // [W][taps] fp32
@@ -203,7 +220,7 @@ struct StackLayer {
   StackTensor ln_w[4], ln_b[4];  // the same four norms as layer norms: weight and bias vectors [W] fp32
   // attention (alone, or the first half of a parallel mixer): w_in rows q | k | v; qf columns follow the same order
   int k_off = 0, v_off = 0;
-  StackTensor qk_norm;   // [H*d + G*d] fp32: gains of the whole-projection query and key norms
+  StackTensor qk_norm;   // [H*d + G*d] fp32: gains of the whole-projection query and key norms; per-head norms: [d + d]
   StackTensor temp_pb;   // [2H] fp32: per-head factor on the score, then per-head bias under the sigmoid
   StackTensor b_o;       // [W] fp32: bias of the output projection
   double *freq = nullptr, *vfreq = nullptr;  // device: rotary frequencies [rot_dims/2] (scaled) and value frequencies [vdim/2]
@@ -213,7 +230,9 @@ struct StackLayer {
   StackTensor a2, a2_b, gla_norm;  // [Hd][rank] compute type, [Hd] fp32, [gla_vdim] fp32
   // feed-forward
   StackTensor w_gu, b_gu, w_down, b_down;  // dense: [2ff][W], [2ff], [W][ff], [W]; experts: stacked per expert
-  StackTensor router;                      // [E][W] fp32
+  StackTensor router;                      // [E][W] fp32; with a shared expert one more row: the logit of its per-token gate
+  StackTensor correction;                  // [E] fp32: added to the sigmoid scores when the experts are chosen
+  StackTensor w_sgu, w_sdown;              // shared expert: [2 shared_ff][W], [W][shared_ff]
 };
 
 // One execution of a layer inside a forward pass.  Without a loop every layer runs once; a looped stretch contributes one
@@ -221,7 +240,7 @@ struct StackLayer {
 struct StackRun {
   int layer = 0;
   int loop_pass = -1;       // t >= 0: the first layer of loop pass t (the loop's input projection runs in front of it)
-  int kv_run = -1;          // latent: the run whose pool this run reads (itself when it owns one)
+  int kv_run = -1;          // latent, attention: the run whose pool(s) this run reads (itself when it owns them)
   void *pool = nullptr;     // latent with a pool of its own: [pages*page_size][kv_rank + rot_dim]
   void *kpool = nullptr, *vpool = nullptr;  // attention: [pages*page_size][G*dim], [..][G*vdim]
   float *state = nullptr;   // lightning / gated linear attention [slots][H][d][dv]; mingru [slots][n]
@@ -263,6 +282,7 @@ struct StackModel {
   // experts
   int *r_idx = nullptr, *counts = nullptr, *perm_tok = nullptr, *where = nullptr, *tiles = nullptr;
   float *r_wt = nullptr, *rows_out = nullptr;
+  float *y2 = nullptr, *r_sg = nullptr;  // shared expert: its output [T][W] and the logit of its per-token gate [T]
   void *moe_x = nullptr;       // bf16 activations in expert row order (per-expert tensor-core products of large passes)
   int *h_counts = nullptr;     // pinned: rows per expert of the layer being run
   int max_tiles = 0;

@@ -16,6 +16,13 @@ engine's description of the model and names every tensor.  Two families exist:
             per-head temperature and bias instead of softmax) and `parallel` (softmax attention with whole-projection
             query/key norms and position-rotated values, beside gated linear attention with a per-channel decay; the two
             outputs are added with fixed weights); feed-forward gelu_tanh(gate) * up.
+  Fakonex   a layer-list decoder of the same engine with RMS norms (gain vectors) before and after every sublayer; its
+            `attention` mixer is grouped-query softmax attention without rotation, with biases on q, k and v, a per-head RMS
+            norm of queries and keys, a causal mask cut into chunks of a fixed number of positions, a learned per-head sink
+            logit in the softmax denominator and a per-head sigmoid gate on the output, and a layer may read an earlier layer's
+            keys and values instead of projecting its own; the feed-forward is a mixture of SiLU-gated experts chosen by a
+            sigmoid router with a correction vector and a limit on the groups of experts a token may use, plus a shared
+            expert behind a sigmoid gate; the logits pass through a tanh soft cap.
 
 The reference has no model loading at all (crates/inference/src/worker.rs:1 is empty).
 """
@@ -69,7 +76,12 @@ class LayerSpec:
     gla_tau: float = 1.0
     mix_scale: float = 1.0
     gla_scale: float = 1.0
-    mlp_act: str = "clamped"  # clamped (with biases) | gelu_tanh (without)
+    mlp_act: str = "clamped"  # clamped (with biases) | gelu_tanh (without) | silu (without)
+    mask_chunk: int = 0  # attention: chunked causal mask (0 = plain causal)
+    route: str = "softmax_top"  # softmax_top | sigmoid_groups
+    route_groups: int = 0
+    route_keep: int = 0
+    shared_ff: int = 0  # mixture of experts: hidden size of the shared expert (0 = none)
 
 
 @dataclass
@@ -81,10 +93,11 @@ class StackSpec:
     layers: List[LayerSpec]
     canon_taps: int = 0
     norm_eps: float = 1e-5
-    norm_kind: str = "rms_scalar"  # rms_scalar | layer
+    norm_kind: str = "rms_scalar"  # rms_scalar | layer | rms
     embed_scale: float = 1.0
     logit_scale: float = 1.0
     loop: Tuple[int, int, int] = (0, 0, 0)  # start, stop, times (times 0 = no loop)
+    logit_softcap: float = 0.0  # c > 0: logits -> c tanh(logits / c)
 
     def layer_runs(self) -> List[int]:
         """Layer index of every layer run of one forward pass, the looped stretch repeated."""
@@ -96,11 +109,11 @@ class StackSpec:
     def tensor_shapes(self) -> Dict[str, Tuple[int, ...]]:
         """Every tensor of the model file, by name."""
         W, out = self.width, {"embed": (self.vocab, self.width), "head": (self.vocab, self.width)}
-        vec = self.norm_kind == "layer"
+        vec = self.norm_kind in ("layer", "rms")
 
         def norm(name):
             out[name] = (W,) if vec else ()
-            if vec:
+            if self.norm_kind == "layer":
                 out[name + ".b"] = (W,)
         norm("final.norm")
         if self.loop[2] > 0:
@@ -120,13 +133,28 @@ class StackSpec:
                             p + "mix.g": (L.width, W), p + "mix.o": (W, L.width)})
             elif L.mixer in ("attention", "parallel"):
                 a = p + ("mix.left." if L.mixer == "parallel" else "mix.")
-                out.update({a + "q": (L.heads * L.dim, W), a + "k": (L.kv_heads * L.dim, W), a + "o": (W, L.heads * L.vdim)})
-                if not L.attn_flags & B.ATTN_V_IS_K:
+                own = L.kv_from < 0  # a layer that reads another layer's cache has nothing of the keys and values
+                out.update({a + "q": (L.heads * L.dim, W), a + "o": (W, L.heads * L.vdim)})
+                if own:
+                    out[a + "k"] = (L.kv_heads * L.dim, W)
+                if own and not L.attn_flags & B.ATTN_V_IS_K:
                     out[a + "v"] = (L.kv_heads * L.vdim, W)
                 if L.attn_flags & B.ATTN_BIAS:
                     out.update({a + "q.b": (L.heads * L.dim,), a + "k.b": (L.kv_heads * L.dim,), a + "o.b": (W,)})
+                if L.attn_flags & B.ATTN_BIAS_QKV:
+                    out[a + "q.b"] = (L.heads * L.dim,)
+                    if own:
+                        out.update({a + "k.b": (L.kv_heads * L.dim,), a + "v.b": (L.kv_heads * L.vdim,)})
                 if L.attn_flags & B.ATTN_QK_NORM:
                     out.update({a + "q.norm": (L.heads * L.dim,), a + "k.norm": (L.kv_heads * L.dim,)})
+                if L.attn_flags & B.ATTN_QK_NORM_HEAD:
+                    out[a + "q.norm"] = (L.dim,)
+                    if own:
+                        out[a + "k.norm"] = (L.dim,)
+                if L.attn_flags & B.ATTN_SINK:
+                    out[a + "sink"] = (L.heads,)
+                if L.attn_flags & B.ATTN_GATE:
+                    out[a + "g"] = (L.heads, W)
                 if L.attn_flags & B.ATTN_SIGMOID:
                     out.update({a + "temp": (L.heads,), a + "pb": (L.heads,)})
                 if L.mixer == "parallel":
@@ -146,7 +174,7 @@ class StackSpec:
             norm(p + "norm2b")
             if self.canon_taps >= 1:
                 out[p + "canon2"] = (W, self.canon_taps)
-            if L.mlp == "dense" and L.mlp_act == "gelu_tanh":
+            if L.mlp == "dense" and L.mlp_act in ("gelu_tanh", "silu"):
                 out.update({p + "mlp.gate": (L.ff, W), p + "mlp.up": (L.ff, W), p + "mlp.down": (W, L.ff)})
             elif L.mlp == "dense":
                 out.update({p + "mlp.gate": (L.ff, W), p + "mlp.gate.b": (L.ff,), p + "mlp.up": (L.ff, W), p + "mlp.up.b": (L.ff,),
@@ -155,6 +183,11 @@ class StackSpec:
                 out[p + "mlp.router"] = (L.experts, W)
                 for e in range(L.experts):
                     out.update({f"{p}mlp.e{e}.gate": (L.ff, W), f"{p}mlp.e{e}.up": (L.ff, W), f"{p}mlp.e{e}.down": (W, L.ff)})
+                if L.route == "sigmoid_groups":
+                    out[p + "mlp.correction"] = (L.experts,)
+                if L.shared_ff > 0:
+                    out.update({p + "mlp.shared.gate": (L.shared_ff, W), p + "mlp.shared.up": (L.shared_ff, W),
+                                p + "mlp.shared.down": (W, L.shared_ff), p + "mlp.shared.sg": (1, W)})
         return out
 
     def c(self, max_ctx: int, max_logit_rows: int, f32: bool):
@@ -177,11 +210,14 @@ class StackSpec:
             c.rot_factor, c.rot_low, c.rot_high, c.rot_original = L.rot_factor, L.rot_low, L.rot_high, L.rot_original
             c.gla_heads, c.gla_dim, c.gla_vdim, c.gla_rank = L.gla_heads, L.gla_dim, L.gla_vdim, L.gla_rank
             c.gla_tau, c.mix_scale, c.gla_scale = L.gla_tau, L.mix_scale, L.gla_scale
-            c.mlp_act = {"clamped": B.ACT_CLAMPED, "gelu_tanh": B.ACT_GELU_TANH}[L.mlp_act]
+            c.mlp_act = {"clamped": B.ACT_CLAMPED, "gelu_tanh": B.ACT_GELU_TANH, "silu": B.ACT_SILU}[L.mlp_act]
+            c.mask_chunk, c.shared_ff = L.mask_chunk, L.shared_ff
+            c.route_kind = {"softmax_top": B.ROUTE_SOFTMAX_TOP, "sigmoid_groups": B.ROUTE_SIGMOID_GROUPS}[L.route]
+            c.route_groups, c.route_keep = L.route_groups, L.route_keep
         sc = B.StackConfig(self.vocab, self.width, len(self.layers), self.canon_taps, max_ctx, max_logit_rows,
                            B.F32 if f32 else B.BF16, self.norm_eps, arr,
-                           {"rms_scalar": B.NORM_RMS_SCALAR, "layer": B.NORM_LAYER}[self.norm_kind],
-                           self.embed_scale, self.logit_scale, *self.loop)
+                           {"rms_scalar": B.NORM_RMS_SCALAR, "layer": B.NORM_LAYER, "rms": B.NORM_RMS}[self.norm_kind],
+                           self.embed_scale, self.logit_scale, *self.loop, self.logit_softcap)
         return sc, keep
 
 
@@ -275,6 +311,53 @@ def motolix_spec(cfg: dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None)
                      "layer", float((cfg.get("embedding") or {}).get("scale", 1.0)), float(cfg.get("logit_scale", 1.0)), loop)
 
 
+def fakonex_spec(cfg: dict) -> StackSpec:
+    """Fakonex's config.json -> StackSpec: every size and constant from the file.  What the file leaves out is off: a mixer
+    without `mask` sees the whole past, a router without `groups` chooses among all experts, a feed-forward without `shared`
+    has no shared expert, a model without `logit_softcap` no cap."""
+    layers = []
+    for i, ly in enumerate(cfg["layers"]):
+        kind, mx = ly["type"], ly["mixer"]
+        if kind != "attention":
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        L = LayerSpec("attention")
+        L.heads, L.kv_heads, L.dim, L.vdim = int(mx["heads"]), int(mx["kv_heads"]), int(mx["dim"]), int(mx["vdim"])
+        if L.heads % L.kv_heads:
+            raise ValueError(f"layer {i}: heads must be a multiple of kv_heads")
+        L.scale = float(mx["scale"])
+        L.attn_flags = B.ATTN_BIAS_QKV | B.ATTN_QK_NORM_HEAD | B.ATTN_SINK | B.ATTN_GATE
+        mask = mx.get("mask") or {}
+        L.mask_chunk = int(mask.get("size", 0))
+        kf = mx.get("kv_from")
+        L.kv_from = -1 if kf is None else int(kf)
+        if L.kv_from >= 0:
+            if L.kv_from >= i or layers[L.kv_from].kv_from >= 0:
+                raise ValueError(f"layer {i}: kv_from must name an earlier layer that projects its own keys and values")
+            src = layers[L.kv_from]
+            if (src.heads, src.kv_heads, src.dim, src.vdim) != (L.heads, L.kv_heads, L.dim, L.vdim):
+                raise ValueError(f"layer {i}: the layer named by kv_from has other head counts or sizes")
+        ml = ly.get("mlp")
+        if ml is not None:
+            if ml.get("kind") != "moe":
+                raise ValueError(f"layer {i}: unknown feed-forward kind {ml.get('kind')!r}")
+            r = ml["router"]
+            L.mlp, L.mlp_act, L.ff = "moe", "silu", int(ml["expert"]["ff"])
+            L.experts, L.top, L.route = int(r["experts"]), int(r["top"]), "sigmoid_groups"
+            gr = r.get("groups")
+            if gr:
+                L.route_groups, L.route_keep = int(gr["count"]), int(gr["keep"])
+                if L.route_groups < 1 or L.experts % L.route_groups or not 1 <= L.route_keep <= L.route_groups:
+                    raise ValueError(f"layer {i}: groups.count must divide experts and 1 <= groups.keep <= groups.count")
+                if L.route_keep * (L.experts // L.route_groups) < L.top:
+                    raise ValueError(f"layer {i}: the kept groups hold fewer experts than top")
+            sh = ml.get("shared")
+            if sh:
+                L.shared_ff = int(sh["ff"])
+        layers.append(L)
+    return StackSpec("Fakonex", int(cfg["vocab"]), int(cfg["width"]), layers, 0, float((cfg.get("norm") or {}).get("eps", 1e-5)),
+                     "rms", logit_softcap=float(cfg.get("logit_softcap") or 0.0))
+
+
 def llama_shape(cfg: dict):
     """A Hugging Face style Llama config.json -> ModelShape."""
     from .worker import ModelShape
@@ -289,6 +372,7 @@ def llama_shape(cfg: dict):
 ARCHITECTURES: Dict[str, Tuple[str, Callable[..., object]]] = {
     "Kidolorn": ("stack", kidolorn_spec),
     "Motolix": ("stack", motolix_spec),
+    "Fakonex": ("stack", fakonex_spec),
     "LlamaForCausalLM": ("llama", llama_shape),
     "llama": ("llama", llama_shape),
 }
@@ -428,6 +512,8 @@ def random_tensors(spec: StackSpec, seed: int = 0, scale: float = 1.0) -> Dict[s
             a = rng.uniform(0.5, 1.5, shape).astype(np.float32)
         elif leaf == "sink":
             a = rng.normal(0, 1.0, shape).astype(np.float32)
+        elif leaf == "correction":
+            a = rng.normal(0, 0.3, shape).astype(np.float32)
         elif leaf == "b":
             a = rng.normal(0, 0.3, shape).astype(np.float32)
         elif name in ("embed",):

@@ -31,7 +31,7 @@ extern "C" {
 #endif
 
 #define DIS_API __attribute__((visibility("default")))
-#define DIS_ABI_VERSION 3 /* 2: 16-byte request ids, logprob on token events / callback, dis_serving_cancel; 3: dis_layer_config and dis_stack_config grew (attention and parallel mixers, layer norms, layer loops) */
+#define DIS_ABI_VERSION 4 /* 2: 16-byte request ids, logprob on token events / callback, dis_serving_cancel; 3: dis_layer_config and dis_stack_config grew (attention and parallel mixers, layer norms, layer loops); 4: they grew again (chunked mask, sink, per-head query/key norm and output gate of attention, shared key/value cache, grouped sigmoid router, shared expert, RMS norms with gain vectors, logit soft cap) */
 
 /* ---- status codes: WorkerError, crates/core/src/error.rs:115-128 ------------------------------ */
 typedef enum dis_status {
@@ -431,11 +431,18 @@ typedef enum dis_mixer_kind {
 } dis_mixer_kind;
 typedef enum dis_mlp_kind { DIS_MLP_NONE = 0, DIS_MLP_DENSE = 1, DIS_MLP_MOE = 2 } dis_mlp_kind;
 /* Feed-forward unit.  CLAMPED: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, +-limit), biases on every
- * matrix.  GELU_TANH: gelu_tanh(g) u, no biases. */
-typedef enum dis_mlp_act { DIS_ACT_CLAMPED = 0, DIS_ACT_GELU_TANH = 1 } dis_mlp_act;
+ * matrix.  GELU_TANH: gelu_tanh(g) u, no biases.  SILU: g sigmoid(g) u, no biases. */
+typedef enum dis_mlp_act { DIS_ACT_CLAMPED = 0, DIS_ACT_GELU_TANH = 1, DIS_ACT_SILU = 2 } dis_mlp_act;
 /* Norms around the sublayers.  RMS_SCALAR: x / rms(x) times one scalar gain (tensor of shape []).  LAYER: (x - mean) / sqrt(var +
- * eps) * w + b with vectors w ("<name>") and b ("<name>.b"). */
-typedef enum dis_norm_kind { DIS_NORM_RMS_SCALAR = 0, DIS_NORM_LAYER = 1 } dis_norm_kind;
+ * eps) * w + b with vectors w ("<name>") and b ("<name>.b").  RMS: x / rms(x) * w with a gain vector w ("<name>"), no bias. */
+typedef enum dis_norm_kind { DIS_NORM_RMS_SCALAR = 0, DIS_NORM_LAYER = 1, DIS_NORM_RMS = 2 } dis_norm_kind;
+/* How a mixture of experts picks and weighs its experts from the fp32 router logits z.
+ * SOFTMAX_TOP: the `top` largest z; weights = softmax over the chosen z.
+ * SIGMOID_GROUPS: s = sigmoid(z); the choice is made on s + "correction" (a vector per layer): the experts form route_groups
+ * contiguous blocks of equal size, a block is ranked by the sum of its top two choice values, only experts of the route_keep best
+ * groups can be chosen, and among those the `top` largest choice scores win; weights = the chosen experts' s divided by their
+ * sum (+ 1e-20). */
+typedef enum dis_route_kind { DIS_ROUTE_SOFTMAX_TOP = 0, DIS_ROUTE_SIGMOID_GROUPS = 1 } dis_route_kind;
 /* dis_layer_config.attn_flags */
 #define DIS_ATTN_SIGMOID   1u   /* weight of a visible key = sigmoid(score * temp[h] + pb[h]) (per-head tensors "temp", "pb"),
                                    not normalised over the keys; without the flag: softmax over the visible keys */
@@ -445,6 +452,13 @@ typedef enum dis_norm_kind { DIS_NORM_RMS_SCALAR = 0, DIS_NORM_LAYER = 1 } dis_n
 #define DIS_ATTN_ROT_V     8u   /* the value at position j is rotated by j over all vdim coordinates (pairs m, m + vdim/2, angle
                                    j * rot_base^(-2m/vdim)) before it is cached, and a head's output at position i is rotated by -i */
 #define DIS_ATTN_BIAS     16u   /* q, k and the output projection carry biases ("q.b", "k.b", "o.b") */
+#define DIS_ATTN_BIAS_QKV 32u   /* q, k and v carry biases ("q.b", "k.b", "v.b"); the output projection has none */
+#define DIS_ATTN_QK_NORM_HEAD 64u /* every head's q and k are divided by their own root mean square over dim and multiplied by
+                                   "q.norm" / "k.norm" of size dim, shared by the heads (before rotation) */
+#define DIS_ATTN_SINK    128u   /* softmax only: the denominator also holds exp("sink"[h]), a per-head term of the denominator alone
+                                   that is not multiplied by the score scale */
+#define DIS_ATTN_GATE    256u   /* head h's output is multiplied by sigmoid(("g" x)[h]), a scalar per (token, head) ("g":
+                                   [heads][width], reading the mixer's input), before the output projection */
 
 typedef struct dis_layer_config {
   int32_t mixer;                 /* dis_mixer_kind */
@@ -452,7 +466,8 @@ typedef struct dis_layer_config {
   int32_t width;                 /* mingru: size of the recurrence */
   int32_t kv_rank, rot_dim;      /* latent: size of the cached latent, size of the rotated query/key part */
   int32_t rot_dims;              /* latent: leading coordinates of the rotated part that are rotated (pairs i, i + rot_dims/2) */
-  int32_t kv_from;               /* latent: layer whose cache this layer reads; -1 = its own */
+  int32_t kv_from;               /* latent, attention: layer whose cache this layer reads (it then has no key / value projections,
+                                    norms or biases of its own, only queries); -1 = its own */
   float rot_base, scale;         /* latent: rotary base; factor on the scores */
   const float *decay;            /* lightning: [heads] */
   int32_t mlp;                   /* dis_mlp_kind */
@@ -473,6 +488,12 @@ typedef struct dis_layer_config {
   float gla_tau;
   float mix_scale, gla_scale;    /* DIS_MIX_PARALLEL: weights of the two halves' outputs */
   int32_t mlp_act;               /* dis_mlp_act */
+  int32_t mask_chunk;            /* attention: > 0: position i sees j <= i only inside its own chunk, floor(i / mask_chunk) ==
+                                    floor(j / mask_chunk), blocks aligned to position 0; 0: every j <= i */
+  int32_t route_kind;            /* dis_route_kind */
+  int32_t route_groups, route_keep; /* SIGMOID_GROUPS: groups of experts (a divisor of experts; 0 or 1 = no groups), groups kept */
+  int32_t shared_ff;             /* mixture of experts: hidden size of a shared expert ("shared.gate/up/down", same unit) that runs
+                                    on all tokens, joining the sum scaled by sigmoid("shared.sg" x) ("shared.sg": [1][width]); 0 = none */
 } dis_layer_config;
 
 typedef struct dis_stack_config {
@@ -490,6 +511,7 @@ typedef struct dis_stack_config {
    * cache and recurrent state.  In front of pass t the residual becomes "loop.in" [x ; x0] + "loop.step"[t], x0 being the scaled
    * embedding ("loop.in": [width][2 width], "loop.step": [loop_times][width]). */
   int32_t loop_start, loop_stop, loop_times;
+  float logit_softcap;           /* c > 0: logits become c tanh(logits / c) (after logit_scale); 0 = none */
 } dis_stack_config;
 
 /* cfg->model is ignored (model_info reports vocab, width, layers and max_ctx of the stack); tensor parallelism and the
