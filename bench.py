@@ -927,6 +927,110 @@ def run_motolix(args):
     return 0
 
 
+def run_fakonex(args):
+    """Prefill and decode throughput of Fakonex (RMS norms, chunk-masked softmax attention with a sink, per-head query/key norm
+    and an output gate, layers that borrow another layer's keys and values, grouped sigmoid router with a shared expert) next
+    to the closest existing layer-list model -- Motolix's attention layers with a dense feed-forward -- and the Llama decoder,
+    at equal width, depth, vocabulary and head geometry; random weights, one GPU, measured like --workload motolix: one pass
+    over `batch` prompts of `prompt_len` tokens, then K decode steps of the batch, timed by the engine's CUDA events around
+    each pass (metadata upload and token read-back included).  Weights exceed L2 at every size."""
+    from distributed_inference_server_b200 import Engine, InferenceParams, ModelShape, WorkerConfig, models
+    from distributed_inference_server_b200.binding import FLAG_NO_GRAPH as B_FLAG_NO_GRAPH
+    sizes = {"w1024": (1024, 4096), "w2048": (2048, 8192)}
+    want = [k for k in (args.sizes.split(",") if args.sizes else sizes) if k in sizes]
+    batch, plen, vocab = args.batch or 8, args.prompt_len, 32000
+    rng = np.random.default_rng(0)
+    out = []
+    clocks = ClockSampler(0)
+    clocks.start()
+    clocks.mark_start()
+    for key in want:
+        W, ff = sizes[key]
+        H = W // 128
+        G = max(1, H // 4)
+        chunk = max(64, plen // 2)
+
+        def att(mask, kv_from=None):
+            mx = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+            if mask:
+                mx["mask"] = {"size": mask}
+            if kv_from is not None:
+                mx["kv_from"] = kv_from
+            return {"type": "attention", "mixer": mx}
+        # 8 experts of the width's size in 4 groups of which 2 are kept, 2 per token, and a shared expert of the same size: three
+        # expert-sized units per token, as many weights read per token as a dense unit of 3 W
+        moe = {"kind": "moe", "expert": {"ff": W}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": W}}
+        variants = {"mixed": [att(chunk), att(chunk), att(chunk, 1), att(chunk, 1)]}
+        if args.per_mixer:
+            variants["own_cache_no_mask"] = [att(0)] * 4
+            variants["own_cache_chunked"] = [att(chunk)] * 4
+        rec = {"size": key, "width": W, "layers": 4, "expert_ff": W, "dense_ff": ff, "vocab": vocab, "batch": batch, "prompt_len": plen, "mask_chunk": chunk}
+        prompts = [rng.integers(0, vocab, plen).tolist() for _ in range(batch)]
+        P = InferenceParams(max_tokens=1 << 20, temperature=0.0)
+        ctx = plen + args.steps + args.warmup + 64
+
+        def measure(eng):
+            slots = [eng.seq_add(p, P) for p in prompts]
+            t_pre = []
+            for it in range(1 + max(1, args.ttft_runs)):
+                if it:
+                    for sl in slots:
+                        eng.seq_remove(sl)
+                    slots = [eng.seq_add(p, P) for p in prompts]
+                eng.step(slots, batch * plen)
+                t_pre.append(eng.status().last_step_ms)
+            for _ in range(args.warmup):
+                eng.decode(slots)
+            k0 = eng.status().kernel_launches
+            ms = 0.0
+            for _ in range(args.steps):
+                eng.decode(slots)
+                ms += eng.status().last_step_ms
+            launches = eng.status().kernel_launches - k0
+            for sl in slots:
+                eng.seq_remove(sl)
+            pre = min(t_pre[1:])
+            return {"prefill_ms": round(pre, 3), "prefill_tokens_per_s": round(batch * plen / pre * 1e3, 1),
+                    "decode_ms_per_step": round(ms / args.steps, 4), "decode_tokens_per_s": round(batch * args.steps / ms * 1e3, 1),
+                    "launches_per_decode_step": launches // max(1, args.steps)}
+
+        def stack_engine(spec):
+            eng = Engine(WorkerConfig(None, max_batch=batch, max_step_tokens=batch * plen, page_size=64, kv_pages=(batch * ctx + 63) // 64,
+                                      stack=spec, context_size=ctx, compute_dtype="bfloat16", flags=B_FLAG_NO_GRAPH if args.no_graph else 0))
+            for name, a in models.random_tensors(spec, seed=1).items():
+                eng.load_named(name, a)
+            eng.finalize()
+            return eng
+        for vname, layers in variants.items():
+            cfg = {"architecture": "Fakonex", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+                   "layers": [dict(json.loads(json.dumps(m)), mlp=moe) for m in layers]}
+            eng = stack_engine(models.fakonex_spec(cfg))
+            rec["fakonex_" + vname] = measure(eng)
+            eng.close()
+        # the closest existing model: Motolix's attention layers (grouped-query attention of the same kernel family, layer norms,
+        # dense gelu feed-forward of 4 W)
+        m_att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                                "rot": {"base": 1000000.0, "dims": 64}}}
+        cfg = {"architecture": "Motolix", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": float(W) ** 0.5},
+               "logit_scale": 0.5, "layers": [dict(json.loads(json.dumps(m_att)), mlp={"kind": "dense", "ff": ff}) for _ in range(4)]}
+        eng = stack_engine(models.motolix_spec(cfg))
+        rec["motolix_attention"] = measure(eng)
+        eng.close()
+        shape = ModelShape(vocab, W, 4, H, G, 128, ff, ctx)
+        eng = Engine(WorkerConfig(shape, max_batch=batch, max_step_tokens=batch * plen, page_size=64, kv_pages=(batch * ctx + 63) // 64 + batch))
+        eng.load_synthetic(1)
+        eng.finalize()
+        rec["llama"] = measure(eng)
+        eng.close()
+        out.append(rec)
+    clocks.mark_end()
+    line = {"metric": "fakonex_vs_closest_models_equal_size", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "dtype": "bf16", "data": "synthetic (random weights, uniform random tokens)", "higher_is_better": True, "sizes": out,
+            "clocks": clocks.stop()}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -945,9 +1049,9 @@ def main():
     ap.add_argument("--nccl-allreduce", action="store_true", help="TP: use NCCL instead of the fused peer-memory exchange (A/B)")
     ap.add_argument("--tp-exchange", choices=["auto", "oneshot", "twoshot", "ll", "wide"], default="auto",
                     help="TP: peer-memory exchange kernel (auto = ll, the flag-in-data row kernel, up to hidden 4096; wide, the same protocol on a (row, column block) grid, above)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "prefix", "kidolorn", "motolix"], help="serving = BASELINE configs[4]; prefix = TTFT with prefix KV reuse (row f2); kidolorn / motolix = that layer-list design beside Llama at equal size")
-    ap.add_argument("--sizes", default="", help="kidolorn, motolix: comma list out of w1024,w2048 (default both)")
-    ap.add_argument("--per-mixer", action="store_true", help="kidolorn, motolix: also four layers of each mixer alone")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "prefix", "kidolorn", "motolix", "fakonex"], help="serving = BASELINE configs[4]; prefix = TTFT with prefix KV reuse (row f2); kidolorn / motolix / fakonex = that layer-list design beside Llama (and its closest layer-list relative) at equal size")
+    ap.add_argument("--sizes", default="", help="kidolorn, motolix, fakonex: comma list out of w1024,w2048 (default both)")
+    ap.add_argument("--per-mixer", action="store_true", help="kidolorn, motolix, fakonex: also four layers of each mixer (fakonex: of each cache / mask arrangement) alone")
     ap.add_argument("--model", default="8b", choices=["8b", "70b"], help="70b = BASELINE configs[3] (TP=8, batch 32)")
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--prefill-budget", type=int, default=0, help="serving: prompt tokens read per scheduler step (0 = library default)")
@@ -969,6 +1073,8 @@ def main():
         return run_kidolorn(args)
     if args.workload == "motolix":
         return run_motolix(args)
+    if args.workload == "fakonex":
+        return run_fakonex(args)
     return run_ours(args)
 
 

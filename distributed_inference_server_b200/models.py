@@ -334,8 +334,8 @@ def fakonex_spec(cfg: dict) -> StackSpec:
             if L.kv_from >= i or layers[L.kv_from].kv_from >= 0:
                 raise ValueError(f"layer {i}: kv_from must name an earlier layer that projects its own keys and values")
             src = layers[L.kv_from]
-            if (src.heads, src.kv_heads, src.dim, src.vdim) != (L.heads, L.kv_heads, L.dim, L.vdim):
-                raise ValueError(f"layer {i}: the layer named by kv_from has other head counts or sizes")
+            if (src.kv_heads, src.dim, src.vdim) != (L.kv_heads, L.dim, L.vdim):
+                raise ValueError(f"layer {i}: the layer named by kv_from has other key/value heads or sizes")
         ml = ly.get("mlp")
         if ml is not None:
             if ml.get("kind") != "moe":

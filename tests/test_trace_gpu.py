@@ -30,6 +30,16 @@ def test_trace_replay_of_a_motolix_model(tmp_path, dtype, tol):
     _replay(tmp_path, dtype, tol, cfg, M.weights(cfg, seed=3), M.oracle_logits)
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", None)])
+def test_trace_replay_of_a_fakonex_model(tmp_path, dtype, tol):
+    """The same schedule through a Fakonex model whose chunks (24, 40, 100 positions) and pages (64) never line up, with a layer
+    that borrows another's keys and values: pages go from request to request under both."""
+    from tests import _fakonex_util as F
+    cfg = F.config([(F.attention(dim=16, vdim=16, chunk=24), F.moe()), (F.attention(dim=16, vdim=16, chunk=100, kv_from=0), F.moe(experts=4, top=2, groups=(2, 1), shared=0)),
+                    (F.attention(heads=3, kv_heads=3, dim=6, vdim=10, chunk=40), None)], vocab=90, width=40)
+    _replay(tmp_path, dtype, tol, cfg, F.weights(cfg, seed=3), F.oracle_logits)
+
+
 def _replay(tmp_path, dtype, tol, cfg, W, oracle_logits):
     model = tmp_path / "model"
     model.mkdir()
