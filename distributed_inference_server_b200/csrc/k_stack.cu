@@ -512,97 +512,171 @@ cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long
 __device__ __forceinline__ float gelu_tanh_(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
-template <bool F32, int ACT>
+template <int ACT>
+__device__ __forceinline__ float glu_unit(float g, float u, float limit) {
+  if (ACT == DIS_ACT_GELU_TANH) return gelu_tanh_(g) * u;
+  if (ACT == DIS_ACT_SILU) return g * sigmoid_precise(g) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * sigmoid_precise(1.702f * g) * (u + 1.f);
+}
+// VEC: ff is a multiple of 4 and every base pointer 16-byte aligned: a thread takes four neighbouring columns (16-byte loads of
+// gate and up, one 8- or 16-byte store)
+template <bool F32, int ACT, bool VEC>
 __global__ void stack_glu_kernel(const float *__restrict__ gu, int n_part, long long stride, const float *__restrict__ bias,
                                  void *__restrict__ act, const int *rows_ptr, int M, int ff, float limit) {
   const int rows = rows_ptr ? min(M, rows_ptr[0]) : M;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const float *gr = gu + (long long)r * 2 * ff;
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) {
-      float g = gr[c] + (bias ? bias[c] : 0.f), u = gr[ff + c] + (bias ? bias[ff + c] : 0.f);
-      for (int k = 1; k < n_part; k++) { g += gr[(long long)k * stride + c]; u += gr[(long long)k * stride + ff + c]; }
-      float v;
-      if (ACT == DIS_ACT_GELU_TANH) v = gelu_tanh_(g) * u;
-      else if (ACT == DIS_ACT_SILU) v = g * sigmoid_precise(g) * u;
-      else {
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-        v = g * sigmoid_precise(1.702f * g) * (u + 1.f);
+    if (VEC) {
+      for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < ff; c += gridDim.y * blockDim.x * 4) {
+        float4 g = *reinterpret_cast<const float4 *>(gr + c), u = *reinterpret_cast<const float4 *>(gr + ff + c);
+        if (bias) {
+          const float4 bg = *reinterpret_cast<const float4 *>(bias + c), bu = *reinterpret_cast<const float4 *>(bias + ff + c);
+          g.x += bg.x; g.y += bg.y; g.z += bg.z; g.w += bg.w; u.x += bu.x; u.y += bu.y; u.z += bu.z; u.w += bu.w;
+        }
+        for (int k = 1; k < n_part; k++) {
+          const float4 pg = *reinterpret_cast<const float4 *>(gr + (long long)k * stride + c);
+          const float4 pu = *reinterpret_cast<const float4 *>(gr + (long long)k * stride + ff + c);
+          g.x += pg.x; g.y += pg.y; g.z += pg.z; g.w += pg.w; u.x += pu.x; u.y += pu.y; u.z += pu.z; u.w += pu.w;
+        }
+        const float v0 = glu_unit<ACT>(g.x, u.x, limit), v1 = glu_unit<ACT>(g.y, u.y, limit), v2 = glu_unit<ACT>(g.z, u.z, limit),
+                    v3 = glu_unit<ACT>(g.w, u.w, limit);
+        if (F32) *reinterpret_cast<float4 *>(reinterpret_cast<float *>(act) + (long long)r * ff + c) = make_float4(v0, v1, v2, v3);
+        else {
+          uint2 o;
+          o.x = (uint32_t)float_to_bf16_bits(v0) | ((uint32_t)float_to_bf16_bits(v1) << 16);
+          o.y = (uint32_t)float_to_bf16_bits(v2) | ((uint32_t)float_to_bf16_bits(v3) << 16);
+          *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(act) + (long long)r * ff + c) = o;
+        }
       }
-      st_el<F32>(act, (long long)r * ff + c, v);
+    } else {
+      for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) {
+        float g = gr[c] + (bias ? bias[c] : 0.f), u = gr[ff + c] + (bias ? bias[ff + c] : 0.f);
+        for (int k = 1; k < n_part; k++) { g += gr[(long long)k * stride + c]; u += gr[(long long)k * stride + ff + c]; }
+        st_el<F32>(act, (long long)r * ff + c, glu_unit<ACT>(g, u, limit));
+      }
     }
   }
 }
 cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, const float *bias, void *act, bool f32, const int *rows_ptr,
                              int M, int ff, float limit, int kind, cudaStream_t st) {
   if (M <= 0) return cudaSuccess;
+  const bool vec = ff % 4 == 0 && stride % 4 == 0 && reinterpret_cast<uintptr_t>(gu) % 16 == 0 && reinterpret_cast<uintptr_t>(act) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(bias) % 16 == 0;
+  const int per = vec ? 4 : 1;
   // few rows: the columns are spread over grid.y as well
-  const dim3 grid(std::min(M, 148 * 16), M >= 512 ? 1 : std::min((ff + 255) / 256, 16));
-  if (kind == DIS_ACT_GELU_TANH) {
-    if (f32) stack_glu_kernel<true, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
-    else stack_glu_kernel<false, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
-  } else if (kind == DIS_ACT_SILU) {
-    if (f32) stack_glu_kernel<true, DIS_ACT_SILU><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
-    else stack_glu_kernel<false, DIS_ACT_SILU><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
-  } else {
-    if (f32) stack_glu_kernel<true, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
-    else stack_glu_kernel<false, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
-  }
+  const dim3 grid(std::min(M, 148 * 16), M >= 512 ? 1 : std::min((ff + 256 * per - 1) / (256 * per), 16));
+#define DIS_GLU(F, A, V) stack_glu_kernel<F, A, V><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit)
+#define DIS_GLU_ACT(A)                     \
+  do {                                     \
+    if (f32 && vec) DIS_GLU(true, A, true); \
+    else if (f32) DIS_GLU(true, A, false);  \
+    else if (vec) DIS_GLU(false, A, true);  \
+    else DIS_GLU(false, A, false);          \
+  } while (0)
+  if (kind == DIS_ACT_GELU_TANH) DIS_GLU_ACT(DIS_ACT_GELU_TANH);
+  else if (kind == DIS_ACT_SILU) DIS_GLU_ACT(DIS_ACT_SILU);
+  else DIS_GLU_ACT(DIS_ACT_CLAMPED);
+#undef DIS_GLU_ACT
+#undef DIS_GLU
   return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------------------ router and expert rows
-// One block of four warps per token: the warps share the experts' fp32 logits against the fp32 router matrix (a warp per expert
-// at a time), then the first warp chooses.  E <= 1024 (logits sit in shared memory).
+// A block of eight warps takes TB tokens.  Logits: a warp owns a router row (fp32) at a time and forms its product with all TB
+// tokens, so a row is fetched once per TB tokens; with W a multiple of 4 a lane reads 16 bytes of the row and 4 elements of
+// every token per step, all loads of a row in flight together.  Choice: warp i then chooses for token i.  E <= 1024 (a token's
+// scores sit in shared memory).
 // DIS_ROUTE_SOFTMAX_TOP: `top` rounds of arg-max over the logits (lowest index wins a tie), weights = softmax over the chosen.
 // DIS_ROUTE_SIGMOID_GROUPS: s = sigmoid(z); choice scores c = s + correction; with groups > 1 the experts form `groups` equal
 // contiguous runs, a run is ranked by the sum of its top two c, and every expert outside the `keep` best runs gets
 // c = -inf; `top` rounds of arg-max over c; weights = the chosen s over their sum (+ 1e-20).
 // extra (or null): one more fp32 row [W] whose product with the token lands in extra_out[t] (the logit of a per-token gate).
+constexpr int kRouteWarps = 8;
 template <bool F32>
-__global__ void __launch_bounds__(128) stack_route_kernel(const void *hc, const float *__restrict__ router, int T, int W, int E, int top,
-                                                          int kind, const float *__restrict__ correction, int groups, int keep,
-                                                          const float *__restrict__ extra, float *extra_out, int *idx, float *wt) {
-  extern __shared__ float zs[];  // [E] logits (sigmoid scores), [E] choice scores, [groups] run scores, [groups] kept flags
+__device__ __forceinline__ void ld_act4(const void *p, long long i, float (&v)[4]) {  // 4 consecutive activations, i % 4 == 0
+  if (F32) {
+    const float4 a = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p) + i);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(p) + i);
+    v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
+    v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+  }
+}
+template <bool F32, int TB>
+__global__ void __launch_bounds__(kRouteWarps * 32) stack_route_kernel(const void *hc, const float *__restrict__ router, int T, int W, int E,
+                                                                       int top, int kind, const float *__restrict__ correction, int groups,
+                                                                       int keep, const float *__restrict__ extra, float *extra_out,
+                                                                       int *idx, float *wt) {
+  extern __shared__ float zs[];  // per token: [E] logits (sigmoid scores), [E] choice scores, [groups] run scores, [groups] kept flags
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  const int t = blockIdx.x;
-  float *z = zs, *c = zs + E, *gs = c + E;
-  for (int e = w; e < E + (extra ? 1 : 0); e += 4) {
+  const int t0 = blockIdx.x * TB, nt = min(TB, T - t0);
+  const int per_tok = 2 * E + 2 * max(groups, 1);
+  const bool vec = (W & 3) == 0;
+  for (int e = w; e < E + (extra ? 1 : 0); e += kRouteWarps) {
     const float *wr = e < E ? router + (long long)e * W : extra;
-    float s = 0.f;
+    float acc[TB];
+#pragma unroll
+    for (int j = 0; j < TB; j++) acc[j] = 0.f;
+    if (vec) {
 #pragma unroll 4
-    for (int i = l; i < W; i += 32) s = fmaf(ld_el<F32>(hc, (long long)t * W + i), wr[i], s);
-    s = warp_sum(s);
-    if (l == 0) {
-      if (e < E) z[e] = s;
-      else extra_out[t] = s;
+      for (int i = l * 4; i < W; i += 128) {
+        const float4 r = *reinterpret_cast<const float4 *>(wr + i);
+#pragma unroll
+        for (int j = 0; j < TB; j++) {
+          if (j < nt) {
+            float v[4];
+            ld_act4<F32>(hc, (long long)(t0 + j) * W + i, v);
+            acc[j] = fmaf(v[0], r.x, fmaf(v[1], r.y, fmaf(v[2], r.z, fmaf(v[3], r.w, acc[j]))));
+          }
+        }
+      }
+    } else {
+      for (int i = l; i < W; i += 32) {
+        const float r = wr[i];
+#pragma unroll
+        for (int j = 0; j < TB; j++)
+          if (j < nt) acc[j] = fmaf(ld_el<F32>(hc, (long long)(t0 + j) * W + i), r, acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < TB; j++) {
+      const float sum = warp_sum(acc[j]);
+      if (l == 0 && j < nt) {
+        if (e < E) zs[j * per_tok + e] = sum;
+        else extra_out[t0 + j] = sum;
+      }
     }
   }
   __syncthreads();
-  const bool sig = kind == DIS_ROUTE_SIGMOID_GROUPS;
-  if (sig) {
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-      const float sv = sigmoid_precise(z[e]);
-      z[e] = sv;
-      c[e] = sv + correction[e];
-    }
-    __syncthreads();
-    if (groups > 1 && keep < groups) {
-      const int per = E / groups;
-      for (int g = threadIdx.x; g < groups; g += blockDim.x) {
-        float a = -INFINITY, b = -INFINITY;  // the two largest of the run
-        for (int j = 0; j < per; j++) {
-          const float v = c[g * per + j];
-          if (v > a) { b = a; a = v; }
-          else if (v > b) b = v;
-        }
-        gs[g] = per > 1 ? a + b : a;
+  // ---- the choice: one warp per token
+  for (int j = w; j < nt; j += kRouteWarps) {
+    const int t = t0 + j;
+    float *z = zs + j * per_tok, *c = z + E, *gs = c + E;
+    const bool sig = kind == DIS_ROUTE_SIGMOID_GROUPS;
+    if (sig) {
+      for (int e = l; e < E; e += 32) {
+        const float sv = sigmoid_precise(z[e]);
+        z[e] = sv;
+        c[e] = sv + correction[e];
       }
-      __syncthreads();
-      int *kept = reinterpret_cast<int *>(gs + groups);  // [groups]
-      for (int g = threadIdx.x; g < groups; g += blockDim.x) kept[g] = 0;
-      __syncthreads();
-      if (w == 0) {
+      __syncwarp();
+      if (groups > 1 && keep < groups) {
+        const int per = E / groups;
+        int *kept = reinterpret_cast<int *>(gs + groups);  // [groups]
+        for (int g = l; g < groups; g += 32) {
+          float a = -INFINITY, b = -INFINITY;  // the two largest of the run
+          for (int k = 0; k < per; k++) {
+            const float v = c[g * per + k];
+            if (v > a) { b = a; a = v; }
+            else if (v > b) b = v;
+          }
+          gs[g] = per > 1 ? a + b : a;
+          kept[g] = 0;
+        }
+        __syncwarp();
         for (int k = 0; k < keep; k++) {  // keep rounds of arg-max over the runs not yet kept (lowest index wins a tie)
           float best = -INFINITY;
           int bi = 0x7fffffff;
@@ -618,39 +692,37 @@ __global__ void __launch_bounds__(128) stack_route_kernel(const void *hc, const 
           if (l == 0 && bi != 0x7fffffff) kept[bi] = 1;
           __syncwarp();
         }
+        for (int e = l; e < E; e += 32)
+          if (!kept[e / per]) c[e] = -INFINITY;
+        __syncwarp();
       }
-      __syncthreads();
-      for (int e = threadIdx.x; e < E; e += blockDim.x)
-        if (!kept[e / per]) c[e] = -INFINITY;
-      __syncthreads();
     }
+    const float *score = sig ? c : z;
+    float *taken = sig ? c : z;
+    float m0 = 0.f, den = 0.f, mine = 0.f;
+    for (int k = 0; k < top; k++) {
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int e = l; e < E; e += 32) {
+        const float v = score[e];
+        if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+      }
+      if (bi == 0x7fffffff) bi = 0;  // nothing left to choose from (the configuration check rules it out)
+      if (k == 0) m0 = best;
+      const float p = sig ? z[bi] : expf(best - m0);
+      den += p;
+      if (l == k % 32) mine = p;  // lane k keeps the k-th weight (top <= 32)
+      __syncwarp();
+      if (l == 0) { idx[(long long)t * top + k] = bi; taken[bi] = -INFINITY; }
+      __syncwarp();
+    }
+    if (l < top) wt[(long long)t * top + l] = sig ? mine / (den + 1e-20f) : mine / den;
   }
-  if (w != 0) return;
-  const float *score = sig ? c : z;
-  float *taken = sig ? c : z;
-  float m0 = 0.f, den = 0.f, mine = 0.f;
-  for (int k = 0; k < top; k++) {
-    float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int e = l; e < E; e += 32) {
-      const float v = score[e];
-      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (bi == 0x7fffffff) bi = 0;  // nothing left to choose from (the configuration check rules it out)
-    if (k == 0) m0 = best;
-    const float p = sig ? z[bi] : expf(best - m0);
-    den += p;
-    if (l == k % 32) mine = p;  // lane k keeps the k-th weight (top <= 32)
-    __syncwarp();
-    if (l == 0) { idx[(long long)t * top + k] = bi; taken[bi] = -INFINITY; }
-    __syncwarp();
-  }
-  if (l < top) wt[(long long)t * top + l] = sig ? mine / (den + 1e-20f) : mine / den;
 }
 cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int kind,
                                const float *correction, int groups, int keep, const float *extra, float *extra_out, int *idx, float *wt,
@@ -658,9 +730,17 @@ cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, in
   if (E > 1024 || top > 32 || top > E) return cudaErrorInvalidValue;
   if (kind == DIS_ROUTE_SIGMOID_GROUPS && (!correction || groups < 0 || (groups > 1 && (E % groups || keep < 1)))) return cudaErrorInvalidValue;
   if (T <= 0) return cudaSuccess;
-  const size_t sh = (size_t)(2 * E + 2 * std::max(groups, 1)) * sizeof(float);
-  if (f32) stack_route_kernel<true><<<T, 128, sh, st>>>(hc, router, T, W, E, top, kind, correction, groups, keep, extra, extra_out, idx, wt);
-  else stack_route_kernel<false><<<T, 128, sh, st>>>(hc, router, T, W, E, top, kind, correction, groups, keep, extra, extra_out, idx, wt);
+  // prompt-sized passes: eight tokens share every fetch of a router row; small passes keep a block per token (more blocks)
+  const int tb = T >= 1024 && (size_t)8 * (2 * E + 2 * std::max(groups, 1)) * sizeof(float) <= 48 * 1024 ? 8 : 1;
+  const size_t sh = (size_t)tb * (2 * E + 2 * std::max(groups, 1)) * sizeof(float);
+  const int grid = (T + tb - 1) / tb, th = kRouteWarps * 32;
+#define DIS_ROUTE(F, B) \
+  stack_route_kernel<F, B><<<grid, th, sh, st>>>(hc, router, T, W, E, top, kind, correction, groups, keep, extra, extra_out, idx, wt)
+  if (f32 && tb == 8) DIS_ROUTE(true, 8);
+  else if (f32) DIS_ROUTE(true, 1);
+  else if (tb == 8) DIS_ROUTE(false, 8);
+  else DIS_ROUTE(false, 1);
+#undef DIS_ROUTE
   return cudaGetLastError();
 }
 
@@ -716,20 +796,24 @@ cudaError_t launch_stack_moe_gather(const void *hc, const int *perm_tok, void *x
 
 // y = sum_k wt_k * (row of choice k) [+ sigmoid(shared_gate[t]) * shared[t]]: the shared expert's output, when there is one,
 // joins here behind its per-token gate
-__global__ void stack_moe_combine_kernel(const float *rows, const int *where, const float *wt, const float *shared,
-                                         const float *shared_gate, float *y, int W, int top) {
+__global__ void stack_moe_combine_kernel(const float *rows, const int *where, const float *wt, const float *shared, int n_part,
+                                         long long stride, const float *shared_gate, float *y, int W, int top) {
   const long long t = blockIdx.x;
   const float sg = shared ? sigmoid_precise(shared_gate[t]) : 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < top; k++) s = fmaf(wt[t * top + k], rows[(long long)where[t * top + k] * W + i], s);
-    if (shared) s = fmaf(sg, shared[t * W + i], s);
+    if (shared) {
+      float v = 0.f;
+      for (int k = 0; k < n_part; k++) v += shared[(long long)k * stride + t * W + i];
+      s = fmaf(sg, v, s);
+    }
     y[t * W + i] = s;
   }
 }
-cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, const float *shared,
-                                     const float *shared_gate, float *y, int T, int W, int top, cudaStream_t st) {
-  stack_moe_combine_kernel<<<T, 256, 0, st>>>(rows, where, wt, shared, shared_gate, y, W, top);
+cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, const float *shared, int n_part,
+                                     long long stride, const float *shared_gate, float *y, int T, int W, int top, cudaStream_t st) {
+  stack_moe_combine_kernel<<<T, 256, 0, st>>>(rows, where, wt, shared, n_part < 1 ? 1 : n_part, stride, shared_gate, y, W, top);
   return cudaGetLastError();
 }
 

@@ -13,16 +13,33 @@ namespace dis {
 // One block per token.  proj row: queries at q_off [H][d], keys at k_off [G][d], values at v_off [G][dv] (unless values are
 // the keys).  `bias` (or null): one entry per column of the projection, added here when the product left it out.
 // kpool == null: the layer reads another layer's cache; only the queries are prepared.
+// n_part > 1: the projection comes as split-K slices (slice stride `stride`); the block first sums its token's row of n_cols
+// columns (and the bias) into shared memory and works from there.  gate_out (or null): receives columns gate_off .. + H of the
+// row (the logits of the output gates, which the attention kernel reads from memory).
 template <bool F32>
-__global__ void __launch_bounds__(128) stack_attn_prep_kernel(const float *proj, long long ld, int q_off, int k_off, int v_off,
+__global__ void __launch_bounds__(128) stack_attn_prep_kernel(const float *proj, long long ld, int n_part, long long stride, int n_cols,
+                                                              int gate_off, float *gate_out, long long ld_gate, int q_off, int k_off, int v_off,
                                                               const float *bias, const float *qn, const float *kn, const double *freq,
                                                               const double *vfreq, StackAttn c, StackSpans sp, float *qf, void *kpool,
                                                               void *vpool, float *vrot, const int *page_table, int max_pages,
                                                               int page_size) {
-  extern __shared__ float tab[];  // cos [half], sin [half], value cos [dv/2], value sin [dv/2], per-head factors [H + G]
+  extern __shared__ float tab[];  // cos [half], sin [half], value cos [dv/2], value sin [dv/2], per-head factors [H + G], summed row
   __shared__ float sh[32];
   const int t = blockIdx.x;
   const float *row = proj + (long long)t * ld;
+  if (n_part > 1) {
+    float *srow = tab + c.rot_dims + c.dv + c.H + c.G;
+    for (int i = threadIdx.x; i < n_cols; i += blockDim.x) {
+      float v = bias ? bias[i] : 0.f;
+      for (int k = 0; k < n_part; k++) v += row[(long long)k * stride + i];
+      srow[i] = v;
+    }
+    row = srow;
+    bias = nullptr;
+    __syncthreads();
+  }
+  if (gate_out)
+    for (int i = threadIdx.x; i < c.H; i += blockDim.x) gate_out[(long long)t * ld_gate + i] = row[gate_off + i];
   const int pos = sp.pos[t], slot = sp.slot[t];
   const int half = c.rot_dims >> 1, vhalf = c.dv >> 1;
   const bool rot_v = (c.flags & DIS_ATTN_ROT_V) != 0, own = kpool != nullptr;
@@ -98,14 +115,22 @@ __global__ void __launch_bounds__(128) stack_attn_prep_kernel(const float *proj,
     st_el<F32>(vpool, prow * nv + i, v);
   }
 }
-cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, int k_off, int v_off, const float *bias, const float *qn,
+cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int n_part, long long stride, int n_cols, int gate_off, float *gate_out,
+                                   long long ld_gate, int q_off, int k_off, int v_off, const float *bias, const float *qn,
                                    const float *kn, const double *freq, const double *vfreq, const StackAttn &c, const StackSpans &sp,
                                    float *qf, void *kpool, void *vpool, float *vrot, bool f32, const int *page_table, int max_pages,
                                    int page_size, cudaStream_t st) {
   if (sp.T <= 0) return cudaSuccess;
-  const size_t sh = (size_t)(c.rot_dims + c.dv + c.H + c.G) * sizeof(float);
-  if (f32) stack_attn_prep_kernel<true><<<sp.T, 128, sh, st>>>(proj, ld, q_off, k_off, v_off, bias, qn, kn, freq, vfreq, c, sp, qf, kpool, vpool, vrot, page_table, max_pages, page_size);
-  else stack_attn_prep_kernel<false><<<sp.T, 128, sh, st>>>(proj, ld, q_off, k_off, v_off, bias, qn, kn, freq, vfreq, c, sp, qf, kpool, vpool, vrot, page_table, max_pages, page_size);
+  if (n_part < 1) n_part = 1;
+  const size_t sh = (size_t)(c.rot_dims + c.dv + c.H + c.G + (n_part > 1 ? n_cols : 0)) * sizeof(float);
+  if (sh > 200 * 1024) return cudaErrorInvalidValue;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(stack_attn_prep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_attn_prep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  }));
+  if (f32) stack_attn_prep_kernel<true><<<sp.T, 128, sh, st>>>(proj, ld, n_part, stride, n_cols, gate_off, gate_out, ld_gate, q_off, k_off, v_off, bias, qn, kn, freq, vfreq, c, sp, qf, kpool, vpool, vrot, page_table, max_pages, page_size);
+  else stack_attn_prep_kernel<false><<<sp.T, 128, sh, st>>>(proj, ld, n_part, stride, n_cols, gate_off, gate_out, ld_gate, q_off, k_off, v_off, bias, qn, kn, freq, vfreq, c, sp, qf, kpool, vpool, vrot, page_table, max_pages, page_size);
   return cudaGetLastError();
 }
 

@@ -36,6 +36,11 @@ void Engine::free_stack() {
   if (stack) {
     if (stack->h_out) cudaFreeHost(stack->h_out);
     if (stack->h_counts) cudaFreeHost(stack->h_counts);
+    for (int i = 0; i < StackModel::kSide; i++) {
+      if (stack->side[i]) cudaStreamDestroy(stack->side[i]);
+      if (stack->ev_join[i]) cudaEventDestroy(stack->ev_join[i]);
+    }
+    if (stack->ev_fork) cudaEventDestroy(stack->ev_fork);
     for (StackTensor *v : stack->views) delete v;
     delete stack;
     stack = nullptr;
@@ -623,6 +628,11 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     if (!M.f32 && stack_tc) {
       ENG_CUDA(alloc(&M.moe_x, rows * W * 2));
       ENG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&M.h_counts), (size_t)max_e * sizeof(int)));
+      ENG_CUDA(cudaEventCreateWithFlags(&M.ev_fork, cudaEventDisableTiming));
+      for (int i = 0; i < StackModel::kSide; i++) {
+        ENG_CUDA(cudaStreamCreateWithFlags(&M.side[i], cudaStreamNonBlocking));
+        ENG_CUDA(cudaEventCreateWithFlags(&M.ev_join[i], cudaEventDisableTiming));
+      }
     }
   }
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.d_out), (size_t)2 * M.max_rows * 4));
@@ -1119,8 +1129,15 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     const int N = L.n_in;
     const float *in_bias = nullptr;  // minGRU adds its projections' biases itself when the product left them out
     const bool is_attn = lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL;
+    // a plain attention mixer's preparation kernel sums the slices of a split-K input projection itself
+    const bool prep_sums = lc.mixer == DIS_MIX_ATTENTION;
     RET_CUDA(gemm(M.hc, f32, W, L.w_in, 0, L.b_in.ptr ? reinterpret_cast<const float *>(L.b_in.ptr) : nullptr, M.proj, T, N, W, cap_tokens,
-                  lc.mixer == DIS_MIX_MINGRU || is_attn ? &in_bias : nullptr));
+                  lc.mixer == DIS_MIX_MINGRU || is_attn ? &in_bias : nullptr, prep_sums));
+    const float *in_src = M.proj;
+    int in_parts = 1;
+    long long in_stride = 0;
+    if (prep_sums && (pend_parts > 1 || pend_bias)) { in_src = pend_src; in_parts = pend_parts; in_stride = pend_stride; in_bias = pend_bias; }
+    pend_parts = 1; pend_bias = nullptr;
     int n_mix = 0;
     const float *o_bias = nullptr;
     if (lc.mixer == DIS_MIX_LIGHTNING) {
@@ -1148,8 +1165,12 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       const float *kn = qkn ? qkn + ((lc.attn_flags & DIS_ATTN_QK_NORM_HEAD) ? (size_t)d : (size_t)H * d) : nullptr;
       const bool own = lc.kv_from < 0;  // else: the keys and values of the layer named by kv_from, as its latest run cached them
       StackRun &KV = M.runs[(size_t)Rn.kv_run];
-      RET_CUDA(launch_stack_attn_prep(M.proj, N, L.q_off, L.k_off, L.v_off, in_bias, qkn, kn, L.freq, L.vfreq, sa, sp, M.qf,
-                                      own ? Rn.kpool : nullptr, own ? Rn.vpool : nullptr, M.vrot, f32, d_page_table, max_pages, page_size, stream));
+      // the gate logits are read by the attention kernel from M.proj: when the projection came as slices the preparation writes
+      // their sums there
+      const bool gated = (lc.attn_flags & DIS_ATTN_GATE) != 0;
+      RET_CUDA(launch_stack_attn_prep(in_src, N, in_parts, in_stride, N, L.g_off, gated && in_src != M.proj ? M.proj + L.g_off : nullptr, N, L.q_off,
+                                      L.k_off, L.v_off, in_bias, qkn, kn, L.freq, L.vfreq, sa, sp, M.qf, own ? Rn.kpool : nullptr,
+                                      own ? Rn.vpool : nullptr, M.vrot, f32, d_page_table, max_pages, page_size, stream));
       const std::pair<int, int> slices = stack_att_plan[(size_t)Rn.layer];
       RET_CUDA(launch_stack_attn(M.qf, KV.kpool, KV.vpool, f32, tpb, tpb ? tpb + H : nullptr, reinterpret_cast<const float *>(L.sink.ptr), sa, sp,
                                  mt.d<int>(mt.o_kb_tok0), mt.d<int>(mt.o_kb_len), stack_kb, single ? 1 : stack_abq, d_page_table, max_pages,
@@ -1264,7 +1285,14 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       // the always-on unit beside the experts: its dense unit first (it borrows the buffers the experts' rows use afterwards);
       // the logit of its per-token gate is one more row of the router matrix, and the combine kernel adds it in
       const bool shared = lc.shared_ff > 0;
-      if (shared) RET_CUDA(dense_ff(L.w_sgu, StackTensor(), L.w_sdown, StackTensor(), lc.shared_ff, lc.mlp_act, lc.limit, M.y2, false));
+      const float *sh_src = M.y2;
+      int sh_parts = 1;
+      long long sh_stride = 0;
+      if (shared) {
+        RET_CUDA(dense_ff(L.w_sgu, StackTensor(), L.w_sdown, StackTensor(), lc.shared_ff, lc.mlp_act, lc.limit, M.y2, true));
+        if (pend_parts > 1) { sh_src = pend_src; sh_parts = pend_parts; sh_stride = pend_stride; }  // the combine kernel sums the slices
+        pend_parts = 1; pend_bias = nullptr;
+      }
       const float *router = reinterpret_cast<const float *>(L.router.ptr);
       RET_CUDA(launch_stack_route(M.hc, f32, router, T, W, E, top, lc.route_kind, reinterpret_cast<const float *>(L.correction.ptr), lc.route_groups,
                                   lc.route_keep, shared ? router + (size_t)E * W : nullptr, M.r_sg, M.r_idx, M.r_wt, stream));
@@ -1276,30 +1304,40 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
         RET_CUDA(cudaMemcpyAsync(M.h_counts, M.counts, (size_t)E * sizeof(int), cudaMemcpyDeviceToHost, stream));
         RET_CUDA(cudaStreamSynchronize(stream));
         kl += 4;
+        // An expert's rows are few against the GPU (its products fill a fraction of the SMs, or one wave and a bit), so the
+        // experts run side by side: the pass's stream forks into kSide more, expert e keeps to stream e mod (kSide + 1) with its
+        // gate | up product, its gated unit and its down product in order, and the streams join in front of the combine kernel.
+        const bool forked = M.side[0] && !getenv("DIS_STACK_MOE_SERIAL");
+        auto lane = [&](int e) { const int k = e % (StackModel::kSide + 1); return forked && k > 0 ? M.side[k - 1] : stream; };
+        if (forked) {
+          RET_CUDA(cudaEventRecord(M.ev_fork, stream));
+          for (int k = 0; k < StackModel::kSide; k++) RET_CUDA(cudaStreamWaitEvent(M.side[k], M.ev_fork, 0));
+        }
         int off = 0;
         for (int e = 0; e < E; e++) {
           const int cnt = M.h_counts[e];
           if (cnt <= 0) continue;
-          TmaMap xm;
+          cudaStream_t es = lane(e);
+          TmaMap xm, am;
           RET_CUDA(make_tma_map_2d(&xm, reinterpret_cast<uint16_t *>(M.moe_x) + (size_t)off * W, (uint64_t)cnt, (uint64_t)W, (uint32_t)gemm_token_tile(cnt)));
           const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(L.w_gu.ptr) + (size_t)e * 2 * ff * W, (uint64_t)2 * ff, (uint64_t)W, 128);
           if (!wm) return cudaErrorInvalidValue;
-          RET_CUDA(launch_gemm_partial(*wm, xm, M.proj + (size_t)off * 2 * ff, cnt, 2 * ff, W, 0, 1, stream));
-          off += cnt; kl++;
+          RET_CUDA(launch_gemm_partial(*wm, xm, M.proj + (size_t)off * 2 * ff, cnt, 2 * ff, W, 0, 1, es));
+          RET_CUDA(launch_stack_glu(M.proj + (size_t)off * 2 * ff, 1, 0, nullptr, reinterpret_cast<uint16_t *>(M.act) + (size_t)off * ff, f32, nullptr, cnt, ff,
+                                    lc.limit, lc.mlp_act, es));
+          RET_CUDA(make_tma_map_2d(&am, reinterpret_cast<uint16_t *>(M.act) + (size_t)off * ff, (uint64_t)cnt, (uint64_t)ff, (uint32_t)gemm_token_tile(cnt)));
+          const TmaMap *dm = stack_map(reinterpret_cast<const uint16_t *>(L.w_down.ptr) + (size_t)e * W * ff, (uint64_t)W, (uint64_t)ff, 128);
+          if (!dm) return cudaErrorInvalidValue;
+          RET_CUDA(launch_gemm_partial(*dm, am, M.rows_out + (size_t)off * W, cnt, W, ff, 0, 1, es));
+          off += cnt; kl += 3;
         }
-        RET_CUDA(launch_stack_glu(M.proj, 1, 0, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
-        off = 0;
-        for (int e = 0; e < E; e++) {
-          const int cnt = M.h_counts[e];
-          if (cnt <= 0) continue;
-          TmaMap xm;
-          RET_CUDA(make_tma_map_2d(&xm, reinterpret_cast<uint16_t *>(M.act) + (size_t)off * ff, (uint64_t)cnt, (uint64_t)ff, (uint32_t)gemm_token_tile(cnt)));
-          const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(L.w_down.ptr) + (size_t)e * W * ff, (uint64_t)W, (uint64_t)ff, 128);
-          if (!wm) return cudaErrorInvalidValue;
-          RET_CUDA(launch_gemm_partial(*wm, xm, M.rows_out + (size_t)off * W, cnt, W, ff, 0, 1, stream));
-          off += cnt; kl++;
-        }
-        RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? M.y2 : nullptr, M.r_sg, M.y, T, W, top, stream));
+        kl--;  // (the count above included one gated-unit launch over all rows)
+        if (forked)
+          for (int k = 0; k < StackModel::kSide; k++) {
+            RET_CUDA(cudaEventRecord(M.ev_join[k], M.side[k]));
+            RET_CUDA(cudaStreamWaitEvent(stream, M.ev_join[k], 0));
+          }
+        RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? sh_src : nullptr, sh_parts, sh_stride, M.r_sg, M.y, T, W, top, stream));
         pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
         continue;
       }
@@ -1317,7 +1355,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       dn.out = M.rows_out; dn.ldo = W; dn.M = rows; dn.N = W; dn.K = ff;
       dn.tiles = M.tiles; dn.max_tiles = tiles_cap;
       RET_CUDA(launch_stack_gemm(dn, stream));
-      RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? M.y2 : nullptr, M.r_sg, M.y, T, W, top, stream));
+      RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? sh_src : nullptr, sh_parts, sh_stride, M.r_sg, M.y, T, W, top, stream));
       kl += 6;
     }
     pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);

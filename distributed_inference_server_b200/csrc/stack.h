@@ -105,7 +105,10 @@ struct StackAttn {
 // unrotated keys; rotated by pos * vfreq[m] over pairs m, m + dv/2 with DIS_ATTN_ROT_V) to the token's row of the pools
 // ([pages*page_size][G*d] and [..][G*dv]); vrot [T][dv] receives cos | sin of the value angles for the output's rotation back.
 // kpool == null: the layer reads another layer's cache -- only the queries are prepared.
-cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, int k_off, int v_off, const float *bias, const float *qn,
+// n_part > 1: proj holds split-K slices (slice stride `stride`) of n_cols columns, summed here with the bias.  gate_out (or
+// null): [T][ld_gate] receives columns gate_off .. + H of every row (the logits of the output gates).
+cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int n_part, long long stride, int n_cols, int gate_off, float *gate_out,
+                                   long long ld_gate, int q_off, int k_off, int v_off, const float *bias, const float *qn,
                                    const float *kn, const double *freq, const double *vfreq, const StackAttn &c, const StackSpans &sp,
                                    float *qf, void *kpool, void *vpool, float *vrot, bool f32, const int *page_table, int max_pages,
                                    int page_size, cudaStream_t st);
@@ -183,9 +186,10 @@ cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, in
 cudaError_t launch_stack_moe_plan(const int *idx, int T, int top, int E, int tile_rows, int *counts, int *perm_tok, int *where,
                                   int *tiles, int max_tiles, cudaStream_t st);
 cudaError_t launch_stack_moe_gather(const void *hc, const int *perm_tok, void *xs, int rows, int W, cudaStream_t st);
-// y[t] = sum_k wt[t][k] * rows[where[t][k]] (+ sigmoid(shared_gate[t]) * shared[t] when shared is given)
-cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, const float *shared,
-                                     const float *shared_gate, float *y, int T, int W, int top, cudaStream_t st);
+// y[t] = sum_k wt[t][k] * rows[where[t][k]] (+ sigmoid(shared_gate[t]) * shared[t] when shared is given; shared may come as
+// n_part split-K slices of stride `stride`, summed here)
+cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, const float *shared, int n_part,
+                                     long long stride, const float *shared_gate, float *y, int T, int W, int top, cudaStream_t st);
 cudaError_t launch_stack_final_norm(const float *x, const int *row_map, const float *g, void *out, bool f32, int R, int W, float eps,
                                     cudaStream_t st);
 // out[m][n] = bias[n] + sum_s part[s][m][n]: the split-K slices of a tensor-core product, with the projection's bias
@@ -285,6 +289,11 @@ struct StackModel {
   float *y2 = nullptr, *r_sg = nullptr;  // shared expert: its output [T][W] and the logit of its per-token gate [T]
   void *moe_x = nullptr;       // bf16 activations in expert row order (per-expert tensor-core products of large passes)
   int *h_counts = nullptr;     // pinned: rows per expert of the layer being run
+  // large passes: the experts' products run side by side on these streams (an expert's gate-up product, gated unit and down
+  // product stay on one stream; the pass's stream forks before them and joins behind them)
+  static constexpr int kSide = 3;
+  cudaStream_t side[kSide] = {nullptr, nullptr, nullptr};
+  cudaEvent_t ev_fork = nullptr, ev_join[kSide] = {nullptr, nullptr, nullptr};
   int max_tiles = 0;
   uint32_t *d_out = nullptr, *h_out = nullptr;  // [max_rows] ids then [max_rows] log-probabilities
 };
