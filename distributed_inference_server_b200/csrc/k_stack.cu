@@ -75,6 +75,17 @@ __global__ void __launch_bounds__(256) stack_gemm_kernel(StackGemm g) {
 // columns and its lanes stride over K eight elements at a time (16-byte loads of bf16 W), so each W element is read once per
 // eight rows; the lanes' partial sums are added across the warp at the end.
 constexpr int kFewK = 1024, kFewRows = 8, kFewCols = 32;
+__device__ __forceinline__ float gelu_tanh_(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// the gated unit of a feed-forward on one (gate, up) pair; kind: dis_mlp_act
+__device__ __forceinline__ float glu_any(int kind, float g, float u, float limit) {
+  if (kind == DIS_ACT_GELU_TANH) return gelu_tanh_(g) * u;
+  if (kind == DIS_ACT_SILU) return g * sigmoid_precise(g) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * sigmoid_precise(1.702f * g) * (u + 1.f);
+}
 template <bool WF32>
 __device__ __forceinline__ void ld_w8(const void *W, long long i, float (&w)[8]) {
   if (WF32) {
@@ -84,6 +95,27 @@ __device__ __forceinline__ void ld_w8(const void *W, long long i, float (&w)[8])
   } else {
     const uint4 v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(W) + i);
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) { w[2 * j] = __uint_as_float(u[j] << 16); w[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
+  }
+}
+// eight consecutive W elements as they come from memory (bf16: 16 bytes in a; float: 32 bytes in a, b), unpacked at use
+template <bool WF32>
+struct FewRaw { uint4 a, b; };
+template <bool WF32>
+__device__ __forceinline__ void ld_raw8(const void *W, long long i, FewRaw<WF32> &r) {
+  if (WF32) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(W) + i);
+    r.a = p[0]; r.b = p[1];
+  } else r.a = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(W) + i);
+}
+template <bool WF32>
+__device__ __forceinline__ void unpack8(const FewRaw<WF32> &r, float (&w)[8]) {
+  if (WF32) {
+    w[0] = __uint_as_float(r.a.x); w[1] = __uint_as_float(r.a.y); w[2] = __uint_as_float(r.a.z); w[3] = __uint_as_float(r.a.w);
+    w[4] = __uint_as_float(r.b.x); w[5] = __uint_as_float(r.b.y); w[6] = __uint_as_float(r.b.z); w[7] = __uint_as_float(r.b.w);
+  } else {
+    const uint32_t u[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
 #pragma unroll
     for (int j = 0; j < 4; j++) { w[2 * j] = __uint_as_float(u[j] << 16); w[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
   }
@@ -112,22 +144,37 @@ __global__ void __launch_bounds__(256) stack_gemm_few_kernel(StackGemm g) {
     float acc[4][kFewRows] = {};
     for (int k0 = 0; k0 < g.K; k0 += kFewK) {
       const int kc = min(kFewK, g.K - k0);
+      // the lane's first 16 bytes of each of its four W rows are requested before A is staged: they travel while the block
+      // gathers its rows, and inside the loop the next step's loads are issued before this step's products
+      FewRaw<WF32> cur[4];
+      auto fetch = [&](int kk, FewRaw<WF32>(&dst)[4]) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          if (n0 + c < g.N) ld_raw8<WF32>(g.W, w_off + (long long)(n0 + c) * g.ldw + k0 + kk, dst[c]);
+          else dst[c].a = dst[c].b = make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      if (l * 8 < kc) fetch(l * 8, cur);
       __syncthreads();
       for (int rr = 0; rr < nr; rr++) {
         const long long a_row = g.a_gather ? g.a_gather[row0 + r0 + rr] : row0 + r0 + rr;
+        if (g.a_glu) {  // A holds gate | up pairs: the row's input is the gated unit, rounded as the compute type would store it
+          const float *ar = reinterpret_cast<const float *>(g.A) + a_off + a_row * g.lda;
+          for (int kk = threadIdx.x; kk < kc; kk += blockDim.x) {
+            const float v = glu_any(g.a_glu - 1, ar[k0 + kk], ar[g.K + k0 + kk], g.a_limit);
+            as[rr][kk] = WF32 ? v : bf16_bits_to_float(float_to_bf16_bits(v));
+          }
+        } else
         for (int kk = threadIdx.x; kk < kc; kk += blockDim.x) as[rr][kk] = ld_el<AF32>(g.A, a_off + a_row * g.lda + k0 + kk);
       }
       __syncthreads();
       for (int kk = l * 8; kk < kc; kk += 256) {
+        FewRaw<WF32> nxt[4];
+        const bool more = kk + 256 < kc;
+        if (more) fetch(kk + 256, nxt);
         float wv[4][8];
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-          if (n0 + c < g.N) ld_w8<WF32>(g.W, w_off + (long long)(n0 + c) * g.ldw + k0 + kk, wv[c]);
-          else {
-#pragma unroll
-            for (int j = 0; j < 8; j++) wv[c][j] = 0.f;
-          }
-        }
+        for (int c = 0; c < 4; c++) unpack8<WF32>(cur[c], wv[c]);
 #pragma unroll
         for (int r = 0; r < kFewRows; r++) {
           if (r < nr) {
@@ -139,6 +186,10 @@ __global__ void __launch_bounds__(256) stack_gemm_few_kernel(StackGemm g) {
 #pragma unroll
               for (int j = 0; j < 8; j++) acc[c][r] = fmaf(av[j], wv[c][j], acc[c][r]);
           }
+        }
+        if (more) {
+#pragma unroll
+          for (int c = 0; c < 4; c++) cur[c] = nxt[c];
         }
       }
     }
@@ -152,12 +203,15 @@ __global__ void __launch_bounds__(256) stack_gemm_few_kernel(StackGemm g) {
   }
 }
 
+// at most 64 rows in all and W rows that 16-byte loads can walk: the few-rows kernel
+bool stack_gemm_few_rows(const StackGemm &g) {
+  const long long wal = g.w_f32 ? 4 : 8;
+  return g.M <= 64 && g.K % 8 == 0 && g.ldw % wal == 0 && g.w_bs % wal == 0 && reinterpret_cast<uintptr_t>(g.W) % 16 == 0;
+}
 cudaError_t launch_stack_gemm(const StackGemm &g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return cudaSuccess;
-  // at most 64 rows in all and W rows that 16-byte loads can walk: the few-rows kernel
-  const long long wal = g.w_f32 ? 4 : 8;
-  const bool few = g.M <= 64 && g.K % 8 == 0 && g.ldw % wal == 0 && g.w_bs % wal == 0 &&
-                   reinterpret_cast<uintptr_t>(g.W) % 16 == 0;
+  const bool few = stack_gemm_few_rows(g);
+  if (g.a_glu && (!few || !g.a_f32)) return cudaErrorInvalidValue;  // the gated input is the few-rows kernel's
   if (few) {
     dim3 grid(g.tiles ? g.max_tiles : (g.M + kStackGemmTile - 1) / kStackGemmTile, (g.N + kFewCols - 1) / kFewCols, g.batch);
     if (grid.x == 0) return cudaSuccess;
@@ -265,12 +319,24 @@ __global__ void __launch_bounds__(256) stack_boundary_ln_kernel(float *x, const 
                                                                 const float *post_w, const float *post_b, const float *pre_w,
                                                                 const float *pre_b, float *hn, void *hc, const float *x0, void *cat,
                                                                 int W, float eps) {
-  extern __shared__ float row[];  // [W]
+  extern __shared__ __align__(16) float row[];  // [W]
   __shared__ float sh[32];
   const long long t = blockIdx.x;
   float *xr = x + t * W;
   if (y) {
     float s = 0.f;
+    if (((W | (int)(stride & 3)) & 3) == 0) {  // four columns per thread and step: 16-byte loads of every slice, all independent
+      for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+        float4 v = bias ? *reinterpret_cast<const float4 *>(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int k = 0; k < n_part; k++) {
+          const float4 p = *reinterpret_cast<const float4 *>(y + (long long)k * stride + t * W + i);
+          v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        *reinterpret_cast<float4 *>(row + i) = v;
+        s += RMS ? (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w) : (v.x + v.y) + (v.z + v.w);
+      }
+    } else
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
       float v = bias ? bias[i] : 0.f;
       for (int k = 0; k < n_part; k++) v += y[(long long)k * stride + t * W + i];
@@ -509,9 +575,6 @@ cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long
 }
 
 // ------------------------------------------------------------------------------------------------ gated units
-__device__ __forceinline__ float gelu_tanh_(float z) {
-  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-}
 template <int ACT>
 __device__ __forceinline__ float glu_unit(float g, float u, float limit) {
   if (ACT == DIS_ACT_GELU_TANH) return gelu_tanh_(g) * u;
@@ -651,7 +714,62 @@ __global__ void __launch_bounds__(kRouteWarps * 32) stack_route_kernel(const voi
     }
   }
   __syncthreads();
-  // ---- the choice: one warp per token
+  // ---- the choice.  Up to 32 experts: one thread per token walks its scores serially (a short chain without shuffles or
+  // barriers; every token of the pass chooses at the same time); more: one warp per token.
+  if (E <= 32) {
+    const int j = threadIdx.x;
+    if (j >= nt) return;
+    const int t = t0 + j;
+    float *z = zs + j * per_tok, *c = z + E, *gs = c + E;
+    const bool sig = kind == DIS_ROUTE_SIGMOID_GROUPS;
+    if (sig) {
+      for (int e = 0; e < E; e++) {
+        const float sv = sigmoid_precise(z[e]);
+        z[e] = sv;
+        c[e] = sv + correction[e];
+      }
+      if (groups > 1 && keep < groups) {
+        const int per = E / groups;
+        for (int g = 0; g < groups; g++) {
+          float a = -INFINITY, b = -INFINITY;  // the two largest of the run
+          for (int k = 0; k < per; k++) {
+            const float v = c[g * per + k];
+            if (v > a) { b = a; a = v; }
+            else if (v > b) b = v;
+          }
+          gs[g] = per > 1 ? a + b : a;
+        }
+        unsigned kept = 0;  // groups <= E <= 32
+        for (int k = 0; k < keep; k++) {
+          float best = -INFINITY;
+          int bi = -1;
+          for (int g = 0; g < groups; g++)
+            if (!((kept >> g) & 1u) && (bi < 0 || gs[g] > best)) { best = gs[g]; bi = g; }
+          if (bi >= 0) kept |= 1u << bi;
+        }
+        for (int e = 0; e < E; e++)
+          if (!((kept >> (e / per)) & 1u)) c[e] = -INFINITY;
+      }
+    }
+    float *score = sig ? c : z;
+    float m0 = 0.f, den = 0.f;
+    for (int k = 0; k < top; k++) {
+      float best = -INFINITY;
+      int bi = -1;
+      for (int e = 0; e < E; e++)
+        if (score[e] > best) { best = score[e]; bi = e; }  // strict: the lowest index wins a tie
+      if (bi < 0) bi = 0;  // nothing left to choose from (the configuration check rules it out)
+      if (k == 0) m0 = best;
+      const float p = sig ? z[bi] : expf(best - m0);
+      den += p;
+      idx[(long long)t * top + k] = bi;
+      wt[(long long)t * top + k] = p;
+      score[bi] = -INFINITY;
+    }
+    const float inv = sig ? 1.f / (den + 1e-20f) : 1.f / den;
+    for (int k = 0; k < top; k++) wt[(long long)t * top + k] *= inv;
+    return;
+  }
   for (int j = w; j < nt; j += kRouteWarps) {
     const int t = t0 + j;
     float *z = zs + j * per_tok, *c = z + E, *gs = c + E;
@@ -800,6 +918,27 @@ __global__ void stack_moe_combine_kernel(const float *rows, const int *where, co
                                          long long stride, const float *shared_gate, float *y, int W, int top) {
   const long long t = blockIdx.x;
   const float sg = shared ? sigmoid_precise(shared_gate[t]) : 0.f;
+  if (((W | (int)(stride & 3)) & 3) == 0) {  // four columns per thread and step, 16-byte accesses
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < top; k++) {
+        const float wk = wt[t * top + k];
+        const float4 r = *reinterpret_cast<const float4 *>(rows + (long long)where[t * top + k] * W + i);
+        s.x = fmaf(wk, r.x, s.x); s.y = fmaf(wk, r.y, s.y); s.z = fmaf(wk, r.z, s.z); s.w = fmaf(wk, r.w, s.w);
+      }
+      if (shared) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int k = 0; k < n_part; k++) {
+          const float4 p = *reinterpret_cast<const float4 *>(shared + (long long)k * stride + t * W + i);
+          v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        s.x = fmaf(sg, v.x, s.x); s.y = fmaf(sg, v.y, s.y); s.z = fmaf(sg, v.z, s.z); s.w = fmaf(sg, v.w, s.w);
+      }
+      *reinterpret_cast<float4 *>(y + t * W + i) = s;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < top; k++) s = fmaf(wt[t * top + k], rows[(long long)where[t * top + k] * W + i], s);

@@ -23,12 +23,24 @@ __global__ void __launch_bounds__(128) stack_attn_prep_kernel(const float *proj,
                                                               const double *vfreq, StackAttn c, StackSpans sp, float *qf, void *kpool,
                                                               void *vpool, float *vrot, const int *page_table, int max_pages,
                                                               int page_size) {
-  extern __shared__ float tab[];  // cos [half], sin [half], value cos [dv/2], value sin [dv/2], per-head factors [H + G], summed row
+  extern __shared__ __align__(16) float tab[];  // cos [half], sin [half], value cos [dv/2], value sin [dv/2], per-head factors [H + G], summed row
+  const int srow_off = (c.rot_dims + c.dv + c.H + c.G + 3) & ~3;  // the summed row starts on a 16-byte boundary
   __shared__ float sh[32];
   const int t = blockIdx.x;
   const float *row = proj + (long long)t * ld;
   if (n_part > 1) {
-    float *srow = tab + c.rot_dims + c.dv + c.H + c.G;
+    float *srow = tab + srow_off;
+    if ((((int)(ld & 3)) | (int)(stride & 3) | (n_cols & 3)) == 0) {  // 16-byte loads of every slice, all independent
+      for (int i = threadIdx.x * 4; i < n_cols; i += blockDim.x * 4) {
+        float4 v = bias ? *reinterpret_cast<const float4 *>(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int k = 0; k < n_part; k++) {
+          const float4 p = *reinterpret_cast<const float4 *>(row + (long long)k * stride + i);
+          v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        *reinterpret_cast<float4 *>(srow + i) = v;
+      }
+    } else
     for (int i = threadIdx.x; i < n_cols; i += blockDim.x) {
       float v = bias ? bias[i] : 0.f;
       for (int k = 0; k < n_part; k++) v += row[(long long)k * stride + i];
@@ -122,7 +134,7 @@ cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int n_part, 
                                    int page_size, cudaStream_t st) {
   if (sp.T <= 0) return cudaSuccess;
   if (n_part < 1) n_part = 1;
-  const size_t sh = (size_t)(c.rot_dims + c.dv + c.H + c.G + (n_part > 1 ? n_cols : 0)) * sizeof(float);
+  const size_t sh = (size_t)(((c.rot_dims + c.dv + c.H + c.G + 3) & ~3) + (n_part > 1 ? n_cols : 0)) * sizeof(float);
   if (sh > 200 * 1024) return cudaErrorInvalidValue;
   static DeviceOnce once;
   DIS_CUDA_TRY(once.run([&] {

@@ -31,8 +31,13 @@ struct StackGemm {
   const int *tiles = nullptr;
   int max_tiles = 0;
   const int *a_gather = nullptr;  // row r of the row space reads A row a_gather[r]
+  // a_glu > 0 (few-rows kernel only, A float): A is [M][2K] gate | up and the product's input is the gated unit (dis_mlp_act
+  // a_glu - 1, clamp a_limit) of each pair, rounded to bf16 when W is bf16 -- the gated-unit kernel folded into the loader
+  int a_glu = 0;
+  float a_limit = 0.f;
 };
 cudaError_t launch_stack_gemm(const StackGemm &g, cudaStream_t st);
+bool stack_gemm_few_rows(const StackGemm &g);  // launch_stack_gemm would take the few-rows kernel
 
 struct StackSpans {  // device arrays of the pass
   const uint32_t *tokens;  // [T]
