@@ -673,19 +673,23 @@ __global__ void __launch_bounds__(kRouteWarps * 32) stack_route_kernel(const voi
                                                                        int top, int kind, const float *__restrict__ correction, int groups,
                                                                        int keep, const float *__restrict__ extra, float *extra_out,
                                                                        int *idx, float *wt) {
-  extern __shared__ float zs[];  // per token: [E] logits (sigmoid scores), [E] choice scores, [groups] run scores, [groups] kept flags
+  extern __shared__ float zs[];  // per token: [E] logits (sigmoid scores), [E] choice scores, [groups] run scores, [groups] kept flags;
+                                 // then [E] correction, [warps][TB] partial sums of the extra row
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   const int t0 = blockIdx.x * TB, nt = min(TB, T - t0);
   const int per_tok = 2 * E + 2 * max(groups, 1);
+  float *corr_s = zs + TB * per_tok, *xpart = corr_s + E;
   const bool vec = (W & 3) == 0;
-  for (int e = w; e < E + (extra ? 1 : 0); e += kRouteWarps) {
-    const float *wr = e < E ? router + (long long)e * W : extra;
-    float acc[TB];
+  // the correction vector comes into shared memory beside the products (the choice below then waits for no global load)
+  if (correction)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) corr_s[e] = correction[e];
+  // row `r` of the router (or the extra row) against the block's tokens over the columns first, first + step, ...: the lane's sums
+  auto row_dot = [&](const float *wr, int first, int step, float (&acc)[TB]) {
 #pragma unroll
     for (int j = 0; j < TB; j++) acc[j] = 0.f;
     if (vec) {
 #pragma unroll 4
-      for (int i = l * 4; i < W; i += 128) {
+      for (int i = first * 4; i < W; i += step * 4) {
         const float4 r = *reinterpret_cast<const float4 *>(wr + i);
 #pragma unroll
         for (int j = 0; j < TB; j++) {
@@ -697,23 +701,38 @@ __global__ void __launch_bounds__(kRouteWarps * 32) stack_route_kernel(const voi
         }
       }
     } else {
-      for (int i = l; i < W; i += 32) {
+      for (int i = first; i < W; i += step) {
         const float r = wr[i];
 #pragma unroll
         for (int j = 0; j < TB; j++)
           if (j < nt) acc[j] = fmaf(ld_el<F32>(hc, (long long)(t0 + j) * W + i), r, acc[j]);
       }
     }
+  };
+  for (int e = w; e < E; e += kRouteWarps) {  // a warp per expert row
+    float acc[TB];
+    row_dot(router + (long long)e * W, l, 32, acc);
 #pragma unroll
     for (int j = 0; j < TB; j++) {
       const float sum = warp_sum(acc[j]);
-      if (l == 0 && j < nt) {
-        if (e < E) zs[j * per_tok + e] = sum;
-        else extra_out[t0 + j] = sum;
-      }
+      if (l == 0 && j < nt) zs[j * per_tok + e] = sum;
+    }
+  }
+  if (extra) {  // the one extra row is shared by all warps (each an eighth of the columns), so that no warp walks a row alone
+    float acc[TB];
+    row_dot(extra, threadIdx.x, kRouteWarps * 32, acc);
+#pragma unroll
+    for (int j = 0; j < TB; j++) {
+      const float sum = warp_sum(acc[j]);
+      if (l == 0) xpart[w * TB + j] = sum;
     }
   }
   __syncthreads();
+  if (extra && threadIdx.x < nt) {
+    float sum = 0.f;
+    for (int k = 0; k < kRouteWarps; k++) sum += xpart[k * TB + threadIdx.x];
+    extra_out[t0 + threadIdx.x] = sum;
+  }
   // ---- the choice.  Up to 32 experts: one thread per token walks its scores serially (a short chain without shuffles or
   // barriers; every token of the pass chooses at the same time); more: one warp per token.
   if (E <= 32) {
@@ -726,7 +745,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) stack_route_kernel(const voi
       for (int e = 0; e < E; e++) {
         const float sv = sigmoid_precise(z[e]);
         z[e] = sv;
-        c[e] = sv + correction[e];
+        c[e] = sv + corr_s[e];
       }
       if (groups > 1 && keep < groups) {
         const int per = E / groups;
@@ -778,7 +797,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) stack_route_kernel(const voi
       for (int e = l; e < E; e += 32) {
         const float sv = sigmoid_precise(z[e]);
         z[e] = sv;
-        c[e] = sv + correction[e];
+        c[e] = sv + corr_s[e];
       }
       __syncwarp();
       if (groups > 1 && keep < groups) {
@@ -849,8 +868,9 @@ cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, in
   if (kind == DIS_ROUTE_SIGMOID_GROUPS && (!correction || groups < 0 || (groups > 1 && (E % groups || keep < 1)))) return cudaErrorInvalidValue;
   if (T <= 0) return cudaSuccess;
   // prompt-sized passes: eight tokens share every fetch of a router row; small passes keep a block per token (more blocks)
-  const int tb = T >= 1024 && (size_t)8 * (2 * E + 2 * std::max(groups, 1)) * sizeof(float) <= 48 * 1024 ? 8 : 1;
-  const size_t sh = (size_t)tb * (2 * E + 2 * std::max(groups, 1)) * sizeof(float);
+  const int per_tok = 2 * E + 2 * std::max(groups, 1);
+  const int tb = T >= 1024 && (size_t)(8 * per_tok + E + 8 * kRouteWarps) * sizeof(float) <= 48 * 1024 ? 8 : 1;
+  const size_t sh = (size_t)(tb * per_tok + E + tb * kRouteWarps) * sizeof(float);
   const int grid = (T + tb - 1) / tb, th = kRouteWarps * 32;
 #define DIS_ROUTE(F, B) \
   stack_route_kernel<F, B><<<grid, th, sh, st>>>(hc, router, T, W, E, top, kind, correction, groups, keep, extra, extra_out, idx, wt)
