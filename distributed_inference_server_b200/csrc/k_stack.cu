@@ -652,9 +652,9 @@ cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, cons
 // every token per step, all loads of a row in flight together.  Choice: warp i then chooses for token i.  E <= 1024 (a token's
 // scores sit in shared memory).
 // DIS_ROUTE_SOFTMAX_TOP: `top` rounds of arg-max over the logits (lowest index wins a tie), weights = softmax over the chosen.
-// DIS_ROUTE_SIGMOID_GROUPS: s = sigmoid(z); choice scores c = s + correction; with groups > 1 the experts form `groups` equal
-// contiguous runs, a run is ranked by the sum of its top two c, and every expert outside the `keep` best runs gets
-// c = -inf; `top` rounds of arg-max over c; weights = the chosen s over their sum (+ 1e-20).
+// DIS_ROUTE_SIGMOID_GROUPS: s = sigmoid(z), c = s + correction; with groups > 1 the expert indices are cut into `groups`
+// contiguous runs, a run is ranked by the sum of its top two c, and experts of runs ranked below `keep` get c = -inf; `top`
+// rounds of arg-max over c; weight of a chosen expert = its s over the chosen experts' sum of s (+ 1e-20).
 // extra (or null): one more fp32 row [W] whose product with the token lands in extra_out[t] (the logit of a per-token gate).
 constexpr int kRouteWarps = 8;
 template <bool F32>

@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
 #pragma unroll
   for (int j = 0; j < DMAX / 8; j++) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f; }
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
-  if (!SIG && sink && blockIdx.z == 0) {  // the sink: the extra term of the denominator, entered once (first slice, one lane of the four)
+  if (!SIG && sink && blockIdx.z == 0) {  // the sink term of the denominator enters as the initial state of the first slice (one lane of the four holds its 1)
 #pragma unroll
     for (int e = 0; e < 2; e++) { mrow[e] = sink[r_head[e]] * kLog2e; lrow[e] = qd == 0 ? 1.f : 0.f; }
   }

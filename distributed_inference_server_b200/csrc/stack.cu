@@ -1282,7 +1282,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       RET_CUDA(dense_ff(L.w_gu, L.b_gu, L.w_down, L.b_down, lc.ff, lc.mlp_act, lc.limit, M.y, later));
     } else {
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
-      // the always-on unit beside the experts: its dense unit first (it borrows the buffers the experts' rows use afterwards);
+      // the always-on unit beside the experts: its dense product first (it borrows the buffers the experts' rows use afterwards);
       // the logit of its per-token gate is one more row of the router matrix, and the combine kernel adds it in
       const bool shared = lc.shared_ff > 0;
       const float *sh_src = M.y2;

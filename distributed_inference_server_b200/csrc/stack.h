@@ -179,9 +179,9 @@ cudaError_t launch_stack_latent_softmax(const float *S, int rows, int ld, const 
 cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, const float *bias, void *act, bool f32, const int *rows_ptr,
                              int M, int ff, float limit, int kind, cudaStream_t st);
 // Router: logits in fp32 from hc and the fp32 router matrix; `top` experts by value (lowest index wins a tie).
-// kind DIS_ROUTE_SOFTMAX_TOP: by logit, weights = softmax over the chosen.  DIS_ROUTE_SIGMOID_GROUPS: by sigmoid(logit) +
-// correction[e] among the experts of the `keep` best of `groups` contiguous runs (a run ranks by the sum of its top two
-// choice scores; groups <= 1: all experts), weights = the chosen sigmoids over their sum (+ 1e-20).
+// kind DIS_ROUTE_SOFTMAX_TOP: by logit, weights = softmax over the chosen.  DIS_ROUTE_SIGMOID_GROUPS: by c = sigmoid(logit) +
+// correction[e], restricted to the `keep` best of `groups` contiguous runs of experts (a run ranks by the sum of its top two c;
+// groups <= 1: no restriction), weights = the chosen sigmoids over their sum (+ 1e-20).
 // extra (or null): one more fp32 row [W]; its product with every token goes to extra_out [T].
 cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int kind,
                                const float *correction, int groups, int keep, const float *extra, float *extra_out, int *idx, float *wt,

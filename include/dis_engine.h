@@ -438,10 +438,10 @@ typedef enum dis_mlp_act { DIS_ACT_CLAMPED = 0, DIS_ACT_GELU_TANH = 1, DIS_ACT_S
 typedef enum dis_norm_kind { DIS_NORM_RMS_SCALAR = 0, DIS_NORM_LAYER = 1, DIS_NORM_RMS = 2 } dis_norm_kind;
 /* How a mixture of experts picks and weighs its experts from the fp32 router logits z.
  * SOFTMAX_TOP: the `top` largest z; weights = softmax over the chosen z.
- * SIGMOID_GROUPS: s = sigmoid(z); the choice is made on s + "correction" (a vector per layer): the experts form route_groups
- * contiguous blocks of equal size, a block is ranked by the sum of its top two choice values, only experts of the route_keep best
- * groups can be chosen, and among those the `top` largest choice scores win; weights = the chosen experts' s divided by their
- * sum (+ 1e-20). */
+ * SIGMOID_GROUPS: s = sigmoid(z) and c = s + "correction" (a vector per layer).  The expert indices are cut into route_groups
+ * contiguous blocks of experts / route_groups each; a block is ranked by c_max1 + c_max2, its top two entries of c; experts of
+ * blocks ranked below route_keep drop out (c = -inf).  The `top` largest remaining c are chosen (ties: lowest index), and
+ * expert e of the chosen set S gets the weight s_e / (sum_{S} s + 1e-20) -- the correction steers the choice only. */
 typedef enum dis_route_kind { DIS_ROUTE_SOFTMAX_TOP = 0, DIS_ROUTE_SIGMOID_GROUPS = 1 } dis_route_kind;
 /* dis_layer_config.attn_flags */
 #define DIS_ATTN_SIGMOID   1u   /* weight of a visible key = sigmoid(score * temp[h] + pb[h]) (per-head tensors "temp", "pb"),
@@ -455,10 +455,10 @@ typedef enum dis_route_kind { DIS_ROUTE_SOFTMAX_TOP = 0, DIS_ROUTE_SIGMOID_GROUP
 #define DIS_ATTN_BIAS_QKV 32u   /* q, k and v carry biases ("q.b", "k.b", "v.b"); the output projection has none */
 #define DIS_ATTN_QK_NORM_HEAD 64u /* every head's q and k are divided by their own root mean square over dim and multiplied by
                                    "q.norm" / "k.norm" of size dim, shared by the heads (before rotation) */
-#define DIS_ATTN_SINK    128u   /* softmax only: the denominator also holds exp("sink"[h]), a per-head term of the denominator alone
-                                   that is not multiplied by the score scale */
-#define DIS_ATTN_GATE    256u   /* head h's output is multiplied by sigmoid(("g" x)[h]), a scalar per (token, head) ("g":
-                                   [heads][width], reading the mixer's input), before the output projection */
+#define DIS_ATTN_SINK    128u   /* softmax only: weights are exp(score_j) / (exp("sink"[h]) + sum_j exp(score_j)) with a per-head tensor
+                                   "sink"; the extra term adds nothing to the numerator and the score scale does not apply to it */
+#define DIS_ATTN_GATE    256u   /* out_h <- out_h * sigmoid(("g" u)[h]) in front of the output projection, u being the mixer's input
+                                   and "g" a [heads][width] matrix: a scalar gate per (token, head) */
 
 typedef struct dis_layer_config {
   int32_t mixer;                 /* dis_mixer_kind */
@@ -488,12 +488,13 @@ typedef struct dis_layer_config {
   float gla_tau;
   float mix_scale, gla_scale;    /* DIS_MIX_PARALLEL: weights of the two halves' outputs */
   int32_t mlp_act;               /* dis_mlp_act */
-  int32_t mask_chunk;            /* attention: > 0: position i sees j <= i only inside its own chunk, floor(i / mask_chunk) ==
-                                    floor(j / mask_chunk), blocks aligned to position 0; 0: every j <= i */
+  int32_t mask_chunk;            /* attention: c > 0: causal attention inside blocks of c consecutive positions aligned to position 0
+                                    of the sequence -- key j is visible to query i iff (i / c) * c <= j <= i; 0: plain causal */
   int32_t route_kind;            /* dis_route_kind */
   int32_t route_groups, route_keep; /* SIGMOID_GROUPS: groups of experts (a divisor of experts; 0 or 1 = no groups), groups kept */
-  int32_t shared_ff;             /* mixture of experts: hidden size of a shared expert ("shared.gate/up/down", same unit) that runs
-                                    on all tokens, joining the sum scaled by sigmoid("shared.sg" x) ("shared.sg": [1][width]); 0 = none */
+  int32_t shared_ff;             /* mixture of experts: hidden size of an always-on unit ("shared.gate/up/down", same form as an
+                                    expert) whose output joins the experts' sum scaled by sigmoid("shared.sg" u), a per-token
+                                    scalar ("shared.sg": [1][width]); 0 = none */
 } dis_layer_config;
 
 typedef struct dis_stack_config {

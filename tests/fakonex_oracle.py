@@ -68,9 +68,9 @@ def gated_unit(P, p, h):
 
 
 def choose_experts(scores, correction, top, groups=None):
-    """Indices of the chosen experts of ONE token, best first.  scores: sigmoid of the router logits [E].  The choice is made
-    on scores + correction; with groups = (count, keep) only the experts of the `keep` best groups take part, a group being
-    E / count consecutive indices and ranked by the sum of its top two choice values."""
+    """Indices of the chosen experts of ONE token, best first.  scores: sigmoid of the router logits [E]; c = scores +
+    correction decides.  groups = (count, keep): indices [g * E/count, (g + 1) * E/count) form block g, a block ranks by the
+    sum of its top two c, and only members of the `keep` best blocks may be picked."""
     c = np.asarray(scores, np.float64) + np.asarray(correction, np.float64)
     E = len(c)
     allowed = np.ones(E, bool)
