@@ -41,6 +41,9 @@ void Engine::free_stack() {
       if (stack->ev_join[i]) cudaEventDestroy(stack->ev_join[i]);
     }
     if (stack->ev_fork) cudaEventDestroy(stack->ev_fork);
+    if (stack->sh_stream) cudaStreamDestroy(stack->sh_stream);
+    if (stack->ev_sh_fork) cudaEventDestroy(stack->ev_sh_fork);
+    if (stack->ev_sh_join) cudaEventDestroy(stack->ev_sh_join);
     for (StackTensor *v : stack->views) delete v;
     delete stack;
     stack = nullptr;
@@ -284,6 +287,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   size_t max_proj = 1, max_mix = 1, max_act = 1, max_qf = 1, max_vrot = 0, max_dec = 0;
   int max_top = 0, max_e = 0;
   bool any_shared = false;
+  size_t max_sff = 0;
   const size_t slots = (size_t)max_batch;
   std::vector<StackTensor *> scalars;
   for (int i = 0; i < sc->n_layers; i++) {
@@ -484,6 +488,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         name(pre + "mlp.shared.sg", &L.router, (size_t)E * W, {1, W}, i);
         max_proj = std::max(max_proj, (size_t)2 * sf);
         max_act = std::max(max_act, (size_t)sf);
+        max_sff = std::max(max_sff, (size_t)sf);
         any_shared = true;
       }
       for (int e = 0; e < E; e++) {
@@ -624,6 +629,18 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     if (any_shared) {
       ENG_CUDA(alloc(reinterpret_cast<void **>(&M.y2), cap * W * 4));
       ENG_CUDA(alloc(reinterpret_cast<void **>(&M.r_sg), cap * 4));
+      const char *lane = getenv("DIS_STACK_SHARED_LANE");  // 0: the shared expert runs in the pass's own stream (A/B runs)
+      if (!(lane && atoi(lane) == 0)) {
+        ENG_CUDA(alloc(reinterpret_cast<void **>(&M.sh_proj), cap * 2 * max_sff * 4));
+        ENG_CUDA(alloc(&M.sh_act, cap * max_sff * esz));
+        if (!M.f32 && stack_tc) {
+          M.sh_scratch_elems = 2 * cap * std::max((size_t)2 * max_sff, (size_t)W);
+          ENG_CUDA(alloc(reinterpret_cast<void **>(&M.sh_scratch), M.sh_scratch_elems * 4));
+        }
+        ENG_CUDA(cudaStreamCreateWithFlags(&M.sh_stream, cudaStreamNonBlocking));
+        ENG_CUDA(cudaEventCreateWithFlags(&M.ev_sh_fork, cudaEventDisableTiming));
+        ENG_CUDA(cudaEventCreateWithFlags(&M.ev_sh_join, cudaEventDisableTiming));
+      }
     }
     if (!M.f32 && stack_tc) {
       ENG_CUDA(alloc(&M.moe_x, rows * W * 2));
@@ -988,6 +1005,13 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   // TMA map cannot describe (K not a multiple of 8), to the fp32-FMA product.  a_rows: rows the buffer behind A holds.
   // later_bias: the caller's next kernel can add the bias itself; it is set to the bias when this product left it out (a
   // single-slice tensor-core product, which has no pass of its own over the result) and to null when it is already in.
+  // The lane a product runs in: its stream and the room for its split-K slices.  Everything runs in the pass's own lane except
+  // a shared expert, which runs beside the router and the experts in a lane of its own (stream, slices, gate | up and
+  // activation buffers), forked off the pass's stream and joined in front of the combine kernel.
+  cudaStream_t cur_st = stream;
+  float *cur_scratch = M.scratch, *cur_proj = M.proj;
+  size_t cur_scratch_elems = M.scratch_elems;
+  void *cur_act = M.act;
   auto gemm = [&](const void *A, bool a_f32, long long lda, const StackTensor &Wt, size_t w_off, const float *bias, float *out,
                   int Mrows, int N, int K, int a_rows = 0, const float **later_bias = nullptr, bool later_sum = false) -> cudaError_t {
     if (later_bias) *later_bias = nullptr;
@@ -997,7 +1021,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(Wt.ptr) + w_off, (uint64_t)N, (uint64_t)K, 128);
       if (!xm || !wm) return cudaErrorInvalidValue;
       int s = gemm_pick_split_k(Mrows, N, K);
-      if ((size_t)s * Mrows * N > M.scratch_elems) s = 1;
+      if ((size_t)s * Mrows * N > cur_scratch_elems) s = 1;
       kl++;
       if (s == 1 && bias && later_bias) { *later_bias = bias; bias = nullptr; }
       if (s == 1 && !bias) {
@@ -1006,18 +1030,18 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
         if (stack_persist && gemm_use_persist(Mrows, N, false)) {
           const TmaMap *xm256 = stack_map(A, (uint64_t)a_rows, (uint64_t)K, 256);
           if (!xm256) return cudaErrorInvalidValue;
-          return launch_gemm_persist_partial(*wm, *xm256, out, Mrows, N, K, 0, stream);
+          return launch_gemm_persist_partial(*wm, *xm256, out, Mrows, N, K, 0, cur_st);
         }
-        return launch_gemm_partial(*wm, *xm, out, Mrows, N, K, 0, 1, stream);
+        return launch_gemm_partial(*wm, *xm, out, Mrows, N, K, 0, 1, cur_st);
       }
-      if ((size_t)s * Mrows * N > M.scratch_elems) return cudaErrorInvalidValue;
-      RET_CUDA(launch_gemm_partial(*wm, *xm, M.scratch, Mrows, N, K, 0, s, stream));
+      if ((size_t)s * Mrows * N > cur_scratch_elems) return cudaErrorInvalidValue;
+      RET_CUDA(launch_gemm_partial(*wm, *xm, cur_scratch, Mrows, N, K, 0, s, cur_st));
       if (later_sum) {  // the boundary kernel of a single-token pass sums the slices and adds the bias
-        pend_parts = s; pend_stride = (long long)Mrows * N; pend_bias = bias; pend_src = M.scratch;
+        pend_parts = s; pend_stride = (long long)Mrows * N; pend_bias = bias; pend_src = cur_scratch;
         return cudaSuccess;
       }
       kl++;
-      return launch_stack_sum_bias(M.scratch, s, (long long)Mrows * N, bias, out, Mrows, N, stream);
+      return launch_stack_sum_bias(cur_scratch, s, (long long)Mrows * N, bias, out, Mrows, N, cur_st);
     }
     StackGemm g;
     g.A = A; g.a_f32 = a_f32; g.lda = lda;
@@ -1025,7 +1049,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     g.w_f32 = Wt.f32; g.ldw = K;
     g.out = out; g.ldo = N; g.bias = bias; g.M = Mrows; g.N = N; g.K = K;
     kl++;
-    return launch_stack_gemm(g, stream);
+    return launch_stack_gemm(g, cur_st);
   };
   RET_CUDA(launch_stack_embed(M.embed.ptr, f32, sp.tokens, M.x, M.x0, M.c.embed_scale, T, W, stream)); kl++;
   const float *pend_y = nullptr, *pend_post = nullptr, *pend_post_b = nullptr;
@@ -1093,26 +1117,26 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
         const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, 256);
         const TmaMap *wm = stack_map(w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, 64);
         if (!xm || !wm) return cudaErrorInvalidValue;
-        RET_CUDA(launch_gemm_persist_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, tc_act, stream));
+        RET_CUDA(launch_gemm_persist_glu(*wm, *xm, reinterpret_cast<uint16_t *>(cur_act), T, ff, W, 0, tc_act, cur_st));
       } else {
         const int tr = 128;
         const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, (uint32_t)gemm_token_tile(T));
         const TmaMap *wm = stack_map(w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, (uint32_t)tr);
         if (!xm || !wm) return cudaErrorInvalidValue;
-        RET_CUDA(launch_gemm_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, tr, tc_act, stream));
+        RET_CUDA(launch_gemm_glu(*wm, *xm, reinterpret_cast<uint16_t *>(cur_act), T, ff, W, 0, tr, tc_act, cur_st));
       }
       kl++;
-      return gemm(M.act, f32, ff, w_down, 0, nullptr, out, T, W, ff, cap_tokens, nullptr, later_ok);
+      return gemm(cur_act, f32, ff, w_down, 0, nullptr, out, T, W, ff, cap_tokens, nullptr, later_ok);
     }
     // the gated unit sums the slices of its input product itself and adds the bias the product left out
     const float *gu_bias = nullptr;
-    RET_CUDA(gemm(M.hc, f32, W, w_gu, 0, reinterpret_cast<const float *>(b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens, &gu_bias, true));
+    RET_CUDA(gemm(M.hc, f32, W, w_gu, 0, reinterpret_cast<const float *>(b_gu.ptr), cur_proj, T, 2 * ff, W, cap_tokens, &gu_bias, true));
     const bool sliced = pend_parts > 1 || pend_bias;
-    RET_CUDA(launch_stack_glu(sliced ? pend_src : M.proj, sliced ? pend_parts : 1, pend_stride, sliced ? pend_bias : gu_bias, M.act, f32, nullptr,
-                              T, ff, limit, act_kind, stream));
+    RET_CUDA(launch_stack_glu(sliced ? pend_src : cur_proj, sliced ? pend_parts : 1, pend_stride, sliced ? pend_bias : gu_bias, cur_act, f32, nullptr,
+                              T, ff, limit, act_kind, cur_st));
     kl++;
     pend_parts = 1; pend_bias = nullptr;
-    return gemm(M.act, f32, ff, w_down, 0, reinterpret_cast<const float *>(b_down.ptr), out, T, W, ff, cap_tokens, nullptr, later_ok);
+    return gemm(cur_act, f32, ff, w_down, 0, reinterpret_cast<const float *>(b_down.ptr), out, T, W, ff, cap_tokens, nullptr, later_ok);
   };
   for (size_t ri = 0; ri < M.runs.size(); ri++) {
     StackRun &Rn = M.runs[ri];
@@ -1288,11 +1312,24 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       const float *sh_src = M.y2;
       int sh_parts = 1;
       long long sh_stride = 0;
+      const bool sh_lane = shared && M.sh_stream != nullptr;
       if (shared) {
-        RET_CUDA(dense_ff(L.w_sgu, StackTensor(), L.w_sdown, StackTensor(), lc.shared_ff, lc.mlp_act, lc.limit, M.y2, true));
+        if (sh_lane) {  // fork: the shared expert's launches go to its own stream and buffers
+          RET_CUDA(cudaEventRecord(M.ev_sh_fork, stream));
+          RET_CUDA(cudaStreamWaitEvent(M.sh_stream, M.ev_sh_fork, 0));
+          cur_st = M.sh_stream; cur_scratch = M.sh_scratch; cur_scratch_elems = M.sh_scratch_elems; cur_proj = M.sh_proj; cur_act = M.sh_act;
+        }
+        const cudaError_t se = dense_ff(L.w_sgu, StackTensor(), L.w_sdown, StackTensor(), lc.shared_ff, lc.mlp_act, lc.limit, M.y2, true);
+        cur_st = stream; cur_scratch = M.scratch; cur_scratch_elems = M.scratch_elems; cur_proj = M.proj; cur_act = M.act;
+        RET_CUDA(se);
         if (pend_parts > 1) { sh_src = pend_src; sh_parts = pend_parts; sh_stride = pend_stride; }  // the combine kernel sums the slices
         pend_parts = 1; pend_bias = nullptr;
       }
+      auto join_shared = [&]() -> cudaError_t {
+        if (!sh_lane) return cudaSuccess;
+        RET_CUDA(cudaEventRecord(M.ev_sh_join, M.sh_stream));
+        return cudaStreamWaitEvent(stream, M.ev_sh_join, 0);
+      };
       const float *router = reinterpret_cast<const float *>(L.router.ptr);
       RET_CUDA(launch_stack_route(M.hc, f32, router, T, W, E, top, lc.route_kind, reinterpret_cast<const float *>(L.correction.ptr), lc.route_groups,
                                   lc.route_keep, shared ? router + (size_t)E * W : nullptr, M.r_sg, M.r_idx, M.r_wt, stream));
@@ -1337,6 +1374,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
             RET_CUDA(cudaEventRecord(M.ev_join[k], M.side[k]));
             RET_CUDA(cudaStreamWaitEvent(stream, M.ev_join[k], 0));
           }
+        RET_CUDA(join_shared());
         RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? sh_src : nullptr, sh_parts, sh_stride, M.r_sg, M.y, T, W, top, stream));
         pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
         continue;
@@ -1359,6 +1397,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
         kl--;
       } else RET_CUDA(launch_stack_glu(M.proj, 1, 0, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
       RET_CUDA(launch_stack_gemm(dn, stream));
+      RET_CUDA(join_shared());
       RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? sh_src : nullptr, sh_parts, sh_stride, M.r_sg, M.y, T, W, top, stream));
       kl += 6;
     }

@@ -299,6 +299,12 @@ struct StackModel {
   static constexpr int kSide = 3;
   cudaStream_t side[kSide] = {nullptr, nullptr, nullptr};
   cudaEvent_t ev_fork = nullptr, ev_join[kSide] = {nullptr, nullptr, nullptr};
+  // a shared expert runs beside the router and the experts: its own stream, split-K slices, gate | up rows and activations
+  cudaStream_t sh_stream = nullptr;
+  cudaEvent_t ev_sh_fork = nullptr, ev_sh_join = nullptr;
+  float *sh_proj = nullptr, *sh_scratch = nullptr;
+  void *sh_act = nullptr;
+  size_t sh_scratch_elems = 0;
   int max_tiles = 0;
   uint32_t *d_out = nullptr, *h_out = nullptr;  // [max_rows] ids then [max_rows] log-probabilities
 };

@@ -449,3 +449,66 @@ def test_greedy_generation_through_the_scheduler():
             seq.append(got[j])
     cb.close()
     e.close()
+
+
+def _random_model(rng):
+    """A made-up configuration: one or two families of (kv heads, dim, vdim) so that later layers can borrow a cache, any chunk
+    length, feed-forwards with and without groups, shared expert and soft cap."""
+    width, vocab = int(rng.choice([48, 64, 96, 128, 200, 50])), int(rng.integers(40, 300))
+    fams = [dict(kv_heads=int(rng.choice([1, 2, 3, 4])), dim=int(rng.choice([8, 16, 24, 32, 64, 12, 20])), vdim=int(rng.choice([16, 32, 64, 8, 24, 40])))
+            for _ in range(int(rng.integers(1, 3)))]
+    layers, owners = [], {}
+    for i in range(int(rng.integers(2, 7))):
+        f = int(rng.integers(0, len(fams)))
+        kv_from = int(rng.choice(owners[f])) if f in owners and rng.random() < 0.5 else None
+        if kv_from is None:
+            owners.setdefault(f, []).append(i)
+        mx = U.attention(heads=fams[f]["kv_heads"] * int(rng.choice([1, 2, 4])), kv_heads=fams[f]["kv_heads"], dim=fams[f]["dim"], vdim=fams[f]["vdim"],
+                         chunk=int(rng.choice([0, 1, 7, 16, 33, 64, 100])), kv_from=kv_from)
+        ml = None
+        if rng.random() < 0.8:
+            E = int(rng.choice([2, 3, 4, 6, 8, 12, 40]))
+            groups, avail = None, E
+            if rng.random() < 0.7:
+                cnt = int(rng.choice([g for g in (1, 2, 3, 4, 6) if E % g == 0]))
+                groups = (cnt, int(rng.integers(1, cnt + 1)))
+                avail = E // cnt * groups[1]
+            ml = U.moe(experts=E, top=int(rng.integers(1, min(avail, 6) + 1)), ff=int(rng.choice([8, 16, 24, 40])), groups=groups,
+                       shared=int(rng.choice([0, 8, 24])))
+        layers.append((mx, ml))
+    return U.config(layers, vocab=vocab, width=width, eps=float(rng.choice([1e-5, 1e-3])), softcap=float(rng.choice([0, 5.0, 30.0])))
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_configurations_and_schedules(seed):
+    """Up to four live requests, random portions beside single tokens, requests left out of a step, a pool that makes pages and
+    slots go round: every position's logits against the oracle."""
+    rng = np.random.default_rng(1000 + seed)
+    cfg = _random_model(rng)
+    W = U.weights(cfg, seed=seed)
+    seqs = {k: toks(int(rng.choice([1, 2, 5, 23, 64, 65, 130, 200])), vocab=cfg["vocab"], seed=seed * 10 + k) for k in range(int(rng.integers(3, 7)))}
+    want = {k: U.oracle_logits(cfg, W, v) for k, v in seqs.items()}
+    page = int(rng.choice([8, 16, 64]))
+    pool = sum((n + page - 1) // page * page for n in sorted((len(v) for v in seqs.values()), reverse=True)[:4]) + page
+    e = U.engine(cfg, W, max_batch=4, pool_tokens=pool, page_size=page, max_step_tokens=pool)
+    f = U.Feeder(e)
+    waiting, live = list(seqs), []
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live.append(waiting.pop(0))
+        step = []
+        for k in live:
+            rem = len(seqs[k]) - f.fed.get(k, 0)
+            if rng.random() < 0.15 and len(live) > 1 and f.fed.get(k, 0) > 0:
+                continue  # left out of this step
+            r = rng.random()
+            step.append((k, seqs[k], 1 if r < 0.4 else int(rng.integers(1, rem + 1)) if r < 0.8 else rem))
+        if not step:
+            continue
+        f.step(step)
+        for k, _, _ in step:
+            if f.fed[k] == len(seqs[k]):
+                assert U.rel_err(f.end(k), want[k]) < 5e-5, (seed, k)
+                live.remove(k)
+    assert e.status().kv_pages_free == e.status().kv_pages_total
+    e.close()
