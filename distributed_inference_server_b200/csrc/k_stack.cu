@@ -323,20 +323,88 @@ __global__ void __launch_bounds__(256) stack_boundary_ln_kernel(float *x, const 
   __shared__ float sh[32];
   const long long t = blockIdx.x;
   float *xr = x + t * W;
-  if (y) {
-    float s = 0.f;
-    if (((W | (int)(stride & 3)) & 3) == 0) {  // four columns per thread and step: 16-byte loads of every slice, all independent
+  if (((W | (int)(stride & 3)) & 3) == 0) {
+    // W a multiple of 4: a thread owns groups of four neighbouring columns through every phase (16-byte accesses to the
+    // slices, the residual, the gains and the outputs; at W = 1024 one group per thread)
+    auto f4 = [](const float *p) { return *reinterpret_cast<const float4 *>(p); };
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (y) {
+      float s = 0.f;
       for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
-        float4 v = bias ? *reinterpret_cast<const float4 *>(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 v = bias ? f4(bias + i) : zero;
 #pragma unroll 4
         for (int k = 0; k < n_part; k++) {
-          const float4 p = *reinterpret_cast<const float4 *>(y + (long long)k * stride + t * W + i);
+          const float4 p = f4(y + (long long)k * stride + t * W + i);
           v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
         }
         *reinterpret_cast<float4 *>(row + i) = v;
         s += RMS ? (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w) : (v.x + v.y) + (v.z + v.w);
       }
-    } else
+      float mean = 0.f, q = 0.f;
+      if (RMS) q = s;
+      else {
+        mean = block_sum(s, sh) / (float)W;
+        for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+          const float4 v = f4(row + i);
+          const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+          q += (a * a + b * b) + (c * c + d * d);
+        }
+      }
+      const float r = rsqrtf(block_sum(q, sh) / (float)W + eps);
+      for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+        const float4 v = f4(row + i), g = f4(post_w + i), b = RMS ? zero : f4(post_b + i);
+        float4 o = f4(xr + i);
+        o.x += (v.x - mean) * r * g.x + b.x; o.y += (v.y - mean) * r * g.y + b.y;
+        o.z += (v.z - mean) * r * g.z + b.z; o.w += (v.w - mean) * r * g.w + b.w;
+        *reinterpret_cast<float4 *>(xr + i) = o;
+        *reinterpret_cast<float4 *>(row + i) = o;
+      }
+    } else {
+      for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) *reinterpret_cast<float4 *>(row + i) = f4(xr + i);
+    }
+    if (cat) {
+      __syncthreads();  // the loop below walks the row column by column
+      for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        st_el<F32>(cat, t * 2 * W + i, row[i]);
+        st_el<F32>(cat, t * 2 * W + W + i, x0[t * W + i]);
+      }
+    }
+    if (!pre_w) return;
+    float s = 0.f;
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {  // each thread re-reads what it wrote itself
+      const float4 v = f4(row + i);
+      s += RMS ? (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w) : (v.x + v.y) + (v.z + v.w);
+    }
+    float mean = 0.f, q = 0.f;
+    if (RMS) q = s;
+    else {
+      mean = block_sum(s, sh) / (float)W;
+      for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+        const float4 v = f4(row + i);
+        const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+        q += (a * a + b * b) + (c * c + d * d);
+      }
+    }
+    const float r = rsqrtf(block_sum(q, sh) / (float)W + eps);
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+      const float4 v = f4(row + i), g = f4(pre_w + i), b = RMS ? zero : f4(pre_b + i);
+      const float4 h = make_float4((v.x - mean) * r * g.x + b.x, (v.y - mean) * r * g.y + b.y, (v.z - mean) * r * g.z + b.z,
+                                   (v.w - mean) * r * g.w + b.w);
+      if (hn) *reinterpret_cast<float4 *>(hn + t * W + i) = h;
+      if (hc) {
+        if (F32) *reinterpret_cast<float4 *>(reinterpret_cast<float *>(hc) + t * W + i) = h;
+        else {
+          uint2 o;
+          o.x = (uint32_t)float_to_bf16_bits(h.x) | ((uint32_t)float_to_bf16_bits(h.y) << 16);
+          o.y = (uint32_t)float_to_bf16_bits(h.z) | ((uint32_t)float_to_bf16_bits(h.w) << 16);
+          *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(hc) + t * W + i) = o;
+        }
+      }
+    }
+    return;
+  }
+  if (y) {
+    float s = 0.f;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
       float v = bias ? bias[i] : 0.f;
       for (int k = 0; k < n_part; k++) v += y[(long long)k * stride + t * W + i];
