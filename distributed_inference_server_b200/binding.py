@@ -34,13 +34,15 @@ class EngineConfig(C.Structure):
                 ("eos_token", C.c_int32), ("stream", C.c_void_p), ("nccl_id", C.c_uint8 * 128)]
 
 
-MIX_LIGHTNING, MIX_MINGRU, MIX_LATENT, MIX_ATTENTION, MIX_PARALLEL = range(5)
+MIX_LIGHTNING, MIX_MINGRU, MIX_LATENT, MIX_ATTENTION, MIX_PARALLEL, MIX_SSM = range(6)
 MLP_NONE, MLP_DENSE, MLP_MOE = range(3)
-ACT_CLAMPED, ACT_GELU_TANH, ACT_SILU = range(3)
+ACT_CLAMPED, ACT_GELU_TANH, ACT_SILU, ACT_RELU2 = range(4)
 NORM_RMS_SCALAR, NORM_LAYER, NORM_RMS = range(3)
-ROUTE_SOFTMAX_TOP, ROUTE_SIGMOID_GROUPS = range(2)
+ROUTE_SOFTMAX_TOP, ROUTE_SIGMOID_GROUPS, ROUTE_SOFTMAX_ALL = range(3)
 ATTN_SIGMOID, ATTN_QK_NORM, ATTN_V_IS_K, ATTN_ROT_V, ATTN_BIAS = 1, 2, 4, 8, 16
-ATTN_BIAS_QKV, ATTN_QK_NORM_HEAD, ATTN_SINK, ATTN_GATE = 32, 64, 128, 256
+ATTN_BIAS_QKV, ATTN_QK_NORM_HEAD, ATTN_SINK, ATTN_GATE, ATTN_SINK_UNIT = 32, 64, 128, 256, 512
+MLP_SHARED_PLAIN = 1
+FRAME_PRE_NORM, FRAME_POS_SINUS, FRAME_LOOP_PLAIN, FRAME_TIED_HEAD = 1, 2, 4, 8
 
 
 class LayerConfig(C.Structure):
@@ -51,14 +53,17 @@ class LayerConfig(C.Structure):
                 ("rot_high", C.c_float), ("rot_original", C.c_int32)] + \
                [(n, C.c_int32) for n in ("gla_heads", "gla_dim", "gla_vdim", "gla_rank")] + \
                [("gla_tau", C.c_float), ("mix_scale", C.c_float), ("gla_scale", C.c_float), ("mlp_act", C.c_int32)] + \
-               [(n, C.c_int32) for n in ("mask_chunk", "route_kind", "route_groups", "route_keep", "shared_ff")]
+               [(n, C.c_int32) for n in ("mask_chunk", "route_kind", "route_groups", "route_keep", "shared_ff", "mask_window")] + \
+               [("score_softcap", C.c_float)] + \
+               [(n, C.c_int32) for n in ("ssm_state", "ssm_groups", "conv_taps", "ssm_norm_groups")] + [("mlp_flags", C.c_uint32)]
 
 
 class StackConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("vocab", "width", "n_layers", "canon_taps", "max_ctx", "max_logit_rows", "compute_dtype")] + \
                [("norm_eps", C.c_float), ("layers", C.POINTER(LayerConfig))] + \
                [("norm_kind", C.c_int32), ("embed_scale", C.c_float), ("logit_scale", C.c_float)] + \
-               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times")] + [("logit_softcap", C.c_float)]
+               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times")] + [("logit_softcap", C.c_float)] + \
+               [("frame_flags", C.c_uint32), ("streams", C.c_int32), ("pos_base", C.c_float)]
 
 
 class SamplingParams(C.Structure):

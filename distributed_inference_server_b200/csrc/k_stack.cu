@@ -247,20 +247,31 @@ cudaError_t launch_stack_sum_bias(const float *part, int n_part, long long strid
 }
 
 // ------------------------------------------------------------------------------------------------ embedding, norms
+// x[t][s] = embed[token] * scale (+ the position vector of the token's position), the same row for every one of the S residual
+// streams.  Position vector: entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i) with f_i = base^(-2i/W) from a table formed in double;
+// the angle is formed and brought into [-pi, pi] in double, sine and cosine of the reduced angle are float.
 template <bool F32>
-__global__ void stack_embed_kernel(const void *embed, const uint32_t *tokens, float *x, float *x0, float scale, int W) {
+__global__ void stack_embed_kernel(const void *embed, const uint32_t *tokens, const int *pos, const double *pos_freq, float *x, float *x0,
+                                   float scale, int W, int S) {
   const long long t = blockIdx.x;
   const long long row = tokens[t];
+  const int p = pos_freq ? pos[t] : 0;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = ld_el<F32>(embed, row * W + i) * scale;
-    x[t * W + i] = v;
+    float v = ld_el<F32>(embed, row * W + i) * scale;
+    if (pos_freq) {
+      const double a = (double)p * pos_freq[i >> 1];
+      const float r = (float)(a - 6.283185307179586476925 * rint(a * 0.15915494309189533577));
+      v += (i & 1) ? cosf(r) : sinf(r);
+    }
+    for (int k = 0; k < S; k++) x[(t * S + k) * W + i] = v;
     if (x0) x0[t * W + i] = v;
   }
 }
-cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, float *x, float *x0, float scale, int T, int W,
-                               cudaStream_t st) {
-  if (f32) stack_embed_kernel<true><<<T, 128, 0, st>>>(embed, tokens, x, x0, scale, W);
-  else stack_embed_kernel<false><<<T, 128, 0, st>>>(embed, tokens, x, x0, scale, W);
+cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, const int *pos, const double *pos_freq, float *x,
+                               float *x0, float scale, int T, int W, int streams, cudaStream_t st) {
+  if (streams < 1) streams = 1;
+  if (f32) stack_embed_kernel<true><<<T, 128, 0, st>>>(embed, tokens, pos, pos_freq, x, x0, scale, W, streams);
+  else stack_embed_kernel<false><<<T, 128, 0, st>>>(embed, tokens, pos, pos_freq, x, x0, scale, W, streams);
   return cudaGetLastError();
 }
 
@@ -471,13 +482,23 @@ cudaError_t launch_stack_boundary_ln(float *x, const float *y, int n_part, long 
   return cudaGetLastError();
 }
 
-// b == null: the RMS form, x / sqrt(mean(x^2) + eps) * w
+// b == null: the RMS form, x / sqrt(mean(x^2) + eps) * w.  S > 1: the row is the sum of the token's S residual streams.
 template <bool F32>
 __global__ void stack_final_ln_kernel(const float *x, const int *row_map, const float *w, const float *b, void *out, int W, float eps,
-                                      float scale) {
+                                      float scale, int S) {
+  extern __shared__ float frow[];  // [W] when S > 1
   __shared__ float sh[32];
   const long long r = blockIdx.x;
-  const float *xr = x + (long long)(row_map ? row_map[r] : r) * W;
+  const float *xr = x + (long long)(row_map ? row_map[r] : r) * S * W;
+  if (S > 1) {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float v = 0.f;
+      for (int k = 0; k < S; k++) v += xr[(long long)k * W + i];
+      frow[i] = v;
+    }
+    __syncthreads();
+    xr = frow;
+  }
   float mean = 0.f, q = 0.f;
   if (b) {
     float s = 0.f;
@@ -489,9 +510,87 @@ __global__ void stack_final_ln_kernel(const float *x, const int *row_map, const 
   for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(out, r * W + i, ((xr[i] - mean) * k * w[i] + (b ? b[i] : 0.f)) * scale);
 }
 cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const float *w, const float *b, void *out, bool f32, int R, int W,
-                                  float eps, float scale, cudaStream_t st) {
-  if (f32) stack_final_ln_kernel<true><<<R, 256, 0, st>>>(x, row_map, w, b, out, W, eps, scale);
-  else stack_final_ln_kernel<false><<<R, 256, 0, st>>>(x, row_map, w, b, out, W, eps, scale);
+                                  float eps, float scale, int streams, cudaStream_t st) {
+  if (streams < 1) streams = 1;
+  const size_t shb = streams > 1 ? (size_t)W * 4 : 0;
+  if (shb > 160 * 1024) return cudaErrorInvalidValue;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(stack_final_ln_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_final_ln_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  }));
+  if (f32) stack_final_ln_kernel<true><<<R, 256, shb, st>>>(x, row_map, w, b, out, W, eps, scale, streams);
+  else stack_final_ln_kernel<false><<<R, 256, shb, st>>>(x, row_map, w, b, out, W, eps, scale, streams);
+  return cudaGetLastError();
+}
+
+// Pre-norm boundary over residual streams, one block per token.  xs [T][S][W].  y = bias + the n_part slices of the product before.
+// prev (or null) = the coefficients of the sublayer that made y, laid out in[S] | out[S] | mix[S][S] (mix indexed [from][to]):
+// every stream becomes x_t <- sum_s mix[s][t] x_s + out[t] y, all from the old streams; prev == null: the one stream gets x += y.
+// Then, with pre_w: u = sum_s next[s] x_s (next = the coming sublayer's coefficients, their first S numbers; null: u = x_0), and
+// h = u / sqrt(mean(u^2) + eps) * pre_w goes to hc in the compute type.  Everything is fp32.
+constexpr int kHcMaxStreams = 8;
+template <bool F32>
+__global__ void __launch_bounds__(256) stack_boundary_hc_kernel(float *xs, int S, const float *y, int n_part, long long stride,
+                                                                const float *bias, const float *prev, const float *next,
+                                                                const float *pre_w, void *hc, int W, float eps) {
+  extern __shared__ __align__(16) float row[];  // [W]: u
+  __shared__ float sh[32];
+  __shared__ float cf[2 * kHcMaxStreams + kHcMaxStreams * kHcMaxStreams];  // out[S] | mix[S][S] of prev, then in[S] of next
+  const long long t = blockIdx.x;
+  float *xr = xs + t * S * W;
+  float *c_out = cf, *c_mix = cf + kHcMaxStreams, *c_in = c_mix + kHcMaxStreams * kHcMaxStreams;
+  if (threadIdx.x < S) {
+    c_out[threadIdx.x] = prev ? prev[S + threadIdx.x] : 1.f;
+    c_in[threadIdx.x] = next ? next[threadIdx.x] : (threadIdx.x == 0 ? 1.f : 0.f);
+  }
+  if (threadIdx.x < S * S) c_mix[threadIdx.x] = prev ? prev[2 * S + threadIdx.x] : (threadIdx.x % (S + 1) == 0 ? 1.f : 0.f);
+  __syncthreads();
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float old[kHcMaxStreams];
+#pragma unroll
+    for (int k = 0; k < kHcMaxStreams; k++) old[k] = k < S ? xr[(long long)k * W + i] : 0.f;
+    float u = 0.f;
+    if (y) {
+      float v = bias ? bias[i] : 0.f;
+      for (int k = 0; k < n_part; k++) v += y[(long long)k * stride + t * W + i];
+#pragma unroll
+      for (int to = 0; to < kHcMaxStreams; to++) {
+        if (to < S) {
+          float nv = c_out[to] * v;
+#pragma unroll
+          for (int from = 0; from < kHcMaxStreams; from++)
+            if (from < S) nv = fmaf(c_mix[from * S + to], old[from], nv);
+          xr[(long long)to * W + i] = nv;
+          u = fmaf(c_in[to], nv, u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < kHcMaxStreams; k++)
+        if (k < S) u = fmaf(c_in[k], old[k], u);
+    }
+    row[i] = u;
+    q += u * u;
+  }
+  if (!pre_w) return;
+  const float r = rsqrtf(block_sum(q, sh) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(hc, t * W + i, row[i] * r * pre_w[i]);  // each thread re-reads what it wrote itself
+}
+cudaError_t launch_stack_boundary_hc(float *xs, int streams, const float *y, int n_part, long long stride, const float *bias,
+                                     const float *prev, const float *next, const float *pre_w, void *hc, bool f32, int T, int W, float eps,
+                                     cudaStream_t st) {
+  if (streams < 1 || streams > kHcMaxStreams || (size_t)W * 4 > 160 * 1024) return cudaErrorInvalidValue;
+  if (T <= 0) return cudaSuccess;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(stack_boundary_hc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_boundary_hc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  }));
+  const size_t shb = (size_t)W * 4;
+  if (f32) stack_boundary_hc_kernel<true><<<T, 256, shb, st>>>(xs, streams, y, n_part < 1 ? 1 : n_part, stride, bias, prev, next, pre_w, hc, W, eps);
+  else stack_boundary_hc_kernel<false><<<T, 256, shb, st>>>(xs, streams, y, n_part < 1 ? 1 : n_part, stride, bias, prev, next, pre_w, hc, W, eps);
   return cudaGetLastError();
 }
 
@@ -645,6 +744,7 @@ cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long
 // ------------------------------------------------------------------------------------------------ gated units
 template <int ACT>
 __device__ __forceinline__ float glu_unit(float g, float u, float limit) {
+  if (ACT == DIS_ACT_RELU2) { const float r = fmaxf(g, 0.f); return r * r; }  // ungated: there is no u
   if (ACT == DIS_ACT_GELU_TANH) return gelu_tanh_(g) * u;
   if (ACT == DIS_ACT_SILU) return g * sigmoid_precise(g) * u;
   g = fminf(g, limit);
@@ -652,23 +752,25 @@ __device__ __forceinline__ float glu_unit(float g, float u, float limit) {
   return g * sigmoid_precise(1.702f * g) * (u + 1.f);
 }
 // VEC: ff is a multiple of 4 and every base pointer 16-byte aligned: a thread takes four neighbouring columns (16-byte loads of
-// gate and up, one 8- or 16-byte store)
+// gate and up, one 8- or 16-byte store).  An ungated activation (DIS_ACT_RELU2) reads rows of ff columns, not 2 ff.
 template <bool F32, int ACT, bool VEC>
 __global__ void stack_glu_kernel(const float *__restrict__ gu, int n_part, long long stride, const float *__restrict__ bias,
                                  void *__restrict__ act, const int *rows_ptr, int M, int ff, float limit) {
   const int rows = rows_ptr ? min(M, rows_ptr[0]) : M;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const float *gr = gu + (long long)r * 2 * ff;
+    constexpr bool GATED = ACT != DIS_ACT_RELU2;
+    const float *gr = gu + (long long)r * (GATED ? 2 : 1) * ff;
     if (VEC) {
       for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < ff; c += gridDim.y * blockDim.x * 4) {
-        float4 g = *reinterpret_cast<const float4 *>(gr + c), u = *reinterpret_cast<const float4 *>(gr + ff + c);
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 g = *reinterpret_cast<const float4 *>(gr + c), u = GATED ? *reinterpret_cast<const float4 *>(gr + ff + c) : zero4;
         if (bias) {
-          const float4 bg = *reinterpret_cast<const float4 *>(bias + c), bu = *reinterpret_cast<const float4 *>(bias + ff + c);
+          const float4 bg = *reinterpret_cast<const float4 *>(bias + c), bu = GATED ? *reinterpret_cast<const float4 *>(bias + ff + c) : zero4;
           g.x += bg.x; g.y += bg.y; g.z += bg.z; g.w += bg.w; u.x += bu.x; u.y += bu.y; u.z += bu.z; u.w += bu.w;
         }
         for (int k = 1; k < n_part; k++) {
           const float4 pg = *reinterpret_cast<const float4 *>(gr + (long long)k * stride + c);
-          const float4 pu = *reinterpret_cast<const float4 *>(gr + (long long)k * stride + ff + c);
+          const float4 pu = GATED ? *reinterpret_cast<const float4 *>(gr + (long long)k * stride + ff + c) : zero4;
           g.x += pg.x; g.y += pg.y; g.z += pg.z; g.w += pg.w; u.x += pu.x; u.y += pu.y; u.z += pu.z; u.w += pu.w;
         }
         const float v0 = glu_unit<ACT>(g.x, u.x, limit), v1 = glu_unit<ACT>(g.y, u.y, limit), v2 = glu_unit<ACT>(g.z, u.z, limit),
@@ -683,8 +785,8 @@ __global__ void stack_glu_kernel(const float *__restrict__ gu, int n_part, long 
       }
     } else {
       for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) {
-        float g = gr[c] + (bias ? bias[c] : 0.f), u = gr[ff + c] + (bias ? bias[ff + c] : 0.f);
-        for (int k = 1; k < n_part; k++) { g += gr[(long long)k * stride + c]; u += gr[(long long)k * stride + ff + c]; }
+        float g = gr[c] + (bias ? bias[c] : 0.f), u = GATED ? gr[ff + c] + (bias ? bias[ff + c] : 0.f) : 0.f;
+        for (int k = 1; k < n_part; k++) { g += gr[(long long)k * stride + c]; if (GATED) u += gr[(long long)k * stride + ff + c]; }
         st_el<F32>(act, (long long)r * ff + c, glu_unit<ACT>(g, u, limit));
       }
     }
@@ -707,6 +809,7 @@ cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, cons
     else DIS_GLU(false, A, false);          \
   } while (0)
   if (kind == DIS_ACT_GELU_TANH) DIS_GLU_ACT(DIS_ACT_GELU_TANH);
+  else if (kind == DIS_ACT_RELU2) DIS_GLU_ACT(DIS_ACT_RELU2);
   else if (kind == DIS_ACT_SILU) DIS_GLU_ACT(DIS_ACT_SILU);
   else DIS_GLU_ACT(DIS_ACT_CLAMPED);
 #undef DIS_GLU_ACT
@@ -933,6 +1036,9 @@ cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, in
                                const float *correction, int groups, int keep, const float *extra, float *extra_out, int *idx, float *wt,
                                cudaStream_t st) {
   if (E > 1024 || top > 32 || top > E) return cudaErrorInvalidValue;
+  // softmax over all experts, then the chosen scores over their sum: the softmax's common factor cancels, and its 1e-20 guard
+  // lies below the last bit of a sum that is at least 1 / E -- the weights are the softmax over the chosen logits
+  if (kind == DIS_ROUTE_SOFTMAX_ALL) kind = DIS_ROUTE_SOFTMAX_TOP;
   if (kind == DIS_ROUTE_SIGMOID_GROUPS && (!correction || groups < 0 || (groups > 1 && (E % groups || keep < 1)))) return cudaErrorInvalidValue;
   if (T <= 0) return cudaSuccess;
   // prompt-sized passes: eight tokens share every fetch of a router row; small passes keep a block per token (more blocks)
@@ -1005,7 +1111,7 @@ cudaError_t launch_stack_moe_gather(const void *hc, const int *perm_tok, void *x
 __global__ void stack_moe_combine_kernel(const float *rows, const int *where, const float *wt, const float *shared, int n_part,
                                          long long stride, const float *shared_gate, float *y, int W, int top) {
   const long long t = blockIdx.x;
-  const float sg = shared ? sigmoid_precise(shared_gate[t]) : 0.f;
+  const float sg = shared ? (shared_gate ? sigmoid_precise(shared_gate[t]) : 1.f) : 0.f;  // no gate: the shared unit joins as it is
   if (((W | (int)(stride & 3)) & 3) == 0) {  // four columns per thread and step, 16-byte accesses
     for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);

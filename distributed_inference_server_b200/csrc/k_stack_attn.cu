@@ -220,10 +220,11 @@ __global__ void __launch_bounds__(kAtWarps * 32) stack_attn_kernel(const float *
   const bool with_sink = !SIG && sink && blockIdx.z == 0;
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) { mx[i] = with_sink ? sink[g * R + i % R] : -INFINITY; dn[i] = with_sink ? 1.f : 0.f; }
   const int *pt = page_table + (long long)slot * max_pages;
-  const int k_lo = c.chunk > 0 ? sp.pos[tok0] / c.chunk * c.chunk : 0;
+  const int k_lo = stack_attn_row_lo(c, sp.pos[tok0]);
   const int k_begin = part ? k_lo + (int)blockIdx.z * keys_per_split : k_lo;
   const int k_end = part ? min(last_pos + 1, k_begin + keys_per_split) : last_pos + 1;
   const long long krow = (long long)c.G * d, vrow = (long long)c.G * dv;
+  const float inv_cap = c.softcap > 0.f ? 1.f / c.softcap : 0.f;
   for (int k0 = k_begin; k0 < k_end; k0 += kAtTile) {
     const int nk = min(kAtTile, k_end - k0);
     __syncthreads();
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(kAtWarps * 32) stack_attn_kernel(const float *
     __syncthreads();
     for (int p = w; p < pairs; p += kAtWarps) {
       const int qpos = sp.pos[tok0 + p / R], h = g * R + p % R;
-      const int qlo = c.chunk > 0 ? qpos / c.chunk * c.chunk : 0;
+      const int qlo = stack_attn_row_lo(c, qpos);
       const float *q = qs + (size_t)p * d;
       float sc = -INFINITY;
       if (l < nk && k0 + l <= qpos && k0 + l >= qlo) {
@@ -253,6 +254,7 @@ __global__ void __launch_bounds__(kAtWarps * 32) stack_attn_kernel(const float *
         }
         for (; i < d; i++) s0 = fmaf(q[i], kr[i], s0);
         sc = ((s0 + s1) + (s2 + s3)) * c.scale;
+        if (c.softcap > 0.f) sc = c.softcap * tanhf(sc * inv_cap);
       }
       float pr, corr = 1.f, psum = 0.f, m_new = 0.f;
       if (SIG) {
@@ -371,10 +373,12 @@ __device__ __forceinline__ float ex2_(float x) {  // 2^x, flushing results below
 // Scores of one 64-key tile -> sigmoid weights, or scaled scores and the rows' running maxima (softmax).  MASKED: the tile
 // reaches past a row's position or the slice's end, or starts before a row's chunk, so every element is checked; interior tiles
 // skip the checks.
+// cap2 > 0 (softmax only): the scaled score s passes cap tanh(s / cap) first; scale2 is then the plain scale over the cap, and
+// tanh x = 1 - 2 / (1 + e^(2x)) is formed with one ex2 and one reciprocal (absolute error of the order of 1e-7, times the cap).
 template <bool SIG, bool MASKED>
 __device__ __forceinline__ void attn_tile_weights(float (&sacc)[kMmKeys / 8][4], float (&mnew)[2], int k0, int qd, const int (&r_pos)[2],
                                                   const int (&r_lo)[2], int k_end, const float (&tmp_h)[2], const float (&pb_h)[2],
-                                                  float scale2) {
+                                                  float scale2, float cap2) {
 #pragma unroll
   for (int j = 0; j < kMmKeys / 8; j++)
 #pragma unroll
@@ -387,7 +391,16 @@ __device__ __forceinline__ void attn_tile_weights(float (&sacc)[kMmKeys / 8][4],
         float rc;
         asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.f + ex2_(-fmaf(sv, tmp_h[e], pb_h[e]))));
         sv = vis ? rc : 0.f;
-      } else { sv = vis ? sv * scale2 : -INFINITY; mnew[e] = fmaxf(mnew[e], sv); }
+      } else {
+        sv *= scale2;
+        if (cap2 > 0.f) {
+          float rc;
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.f + ex2_(sv * (2.f * kLog2e))));
+          sv = cap2 * fmaf(-2.f, rc, 1.f);
+        }
+        sv = vis ? sv : -INFINITY;
+        mnew[e] = fmaxf(mnew[e], sv);
+      }
       sacc[j][q4] = sv;
     }
 }
@@ -415,8 +428,8 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, qd = lane & 3;
   const int slot = sp.slot[tok0], pos_first = sp.pos[tok0], last_pos = pos_first + nq - 1;
   const int *pt = page_table + (long long)slot * max_pages;
-  // chunked mask: the first token's chunk is where the block's history starts (later rows may start later still)
-  const int k_lo = c.chunk > 0 ? pos_first / c.chunk * c.chunk : 0;
+  // chunked or windowed mask: the first token's bound is where the block's history starts (later rows may start later still)
+  const int k_lo = stack_attn_row_lo(c, pos_first);
   const int k_begin = part ? k_lo + (int)blockIdx.z * keys_per_split : k_lo;
   const int k_end = part ? min(last_pos + 1, k_begin + keys_per_split) : last_pos + 1;
   const int nk16 = (d + 15) >> 4, nv8 = dv >> 3, dc = d >> 3, vc = dv >> 3;  // k-steps of Q K^T, n-tiles of P V, 16-byte chunks per row
@@ -434,7 +447,7 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
     r_tok[e] = tok0 + (r_ok[e] ? r / R : 0);
     r_head[e] = kvh * R + (r_ok[e] ? r % R : 0);
     r_pos[e] = r_ok[e] ? pos_first + r / R : -1;
-    r_lo[e] = c.chunk > 0 && r_ok[e] ? r_pos[e] / c.chunk * c.chunk : 0;
+    r_lo[e] = r_ok[e] ? stack_attn_row_lo(c, r_pos[e]) : 0;
   }
 #pragma unroll
   for (int ks = 0; ks < DMAX / 16; ks++) {
@@ -466,12 +479,14 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
 #pragma unroll
     for (int e = 0; e < 2; e++) { tmp_h[e] = temp[r_head[e]] * c.scale * kLog2e; pb_h[e] = pb[r_head[e]] * kLog2e; }
   }
-  const float scale2 = c.scale * kLog2e;
+  // with a soft cap the scores are first brought to units of the cap (scale / cap), and the capped score to units of log 2
+  const float cap2 = !SIG && c.softcap > 0.f ? c.softcap * kLog2e : 0.f;
+  const float scale2 = cap2 > 0.f ? c.scale / c.softcap : c.scale * kLog2e;
   const bool warp_live = warp * 16 < rows;
   const int warp_last_pos = pos_first + min(rows - 1, warp * 16 + 15) / R;
   const int warp_first_pos = pos_first + (warp * 16) / R;
-  const int warp_lo = c.chunk > 0 ? warp_first_pos / c.chunk * c.chunk : 0;        // first key any row of the warp sees
-  const int warp_lo_max = c.chunk > 0 ? warp_last_pos / c.chunk * c.chunk : 0;     // first key every row of the warp sees
+  const int warp_lo = stack_attn_row_lo(c, warp_first_pos);        // first key any row of the warp sees
+  const int warp_lo_max = stack_attn_row_lo(c, warp_last_pos);     // first key every row of the warp sees
   const long long krow = (long long)c.G * d, vrow = (long long)c.G * dv;
   const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks), vs_base = (uint32_t)__cvta_generic_to_shared(Vs);
   // two threads per key row: one page-table read per thread and tile, then the row's 16-byte chunks alternate between the two
@@ -527,8 +542,8 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
       // exponential is one ex2.  Only a tile that reaches past a row's position or the slice's end needs the mask.
       const bool masked = k0 + kMmKeys - 1 > warp_first_pos || k0 + kMmKeys > k_end || k0 < warp_lo_max;
       float mnew[2] = {mrow[0], mrow[1]};
-      if (masked) attn_tile_weights<SIG, true>(sacc, mnew, k0, qd, r_pos, r_lo, k_end, tmp_h, pb_h, scale2);
-      else attn_tile_weights<SIG, false>(sacc, mnew, k0, qd, r_pos, r_lo, k_end, tmp_h, pb_h, scale2);
+      if (masked) attn_tile_weights<SIG, true>(sacc, mnew, k0, qd, r_pos, r_lo, k_end, tmp_h, pb_h, scale2, cap2);
+      else attn_tile_weights<SIG, false>(sacc, mnew, k0, qd, r_pos, r_lo, k_end, tmp_h, pb_h, scale2, cap2);
       if (!SIG) {
         float corr[2];
 #pragma unroll
@@ -633,7 +648,7 @@ cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vp
                               float out_scale, const float *vrot, const float *gate, long long ld_gate, int n_split,
                               int keys_per_split, float *part, cudaStream_t st) {
   if (n_qb <= 0) return cudaSuccess;
-  if (!(c.flags & DIS_ATTN_SINK)) sink = nullptr;
+  if (!(c.flags & (DIS_ATTN_SINK | DIS_ATTN_SINK_UNIT))) sink = nullptr;  // the unit sink is a vector of zero logits
   if (!(c.flags & DIS_ATTN_GATE)) gate = nullptr;
   if (n_split <= 1 || !part) { n_split = 1; part = nullptr; }
   if (n_split > kAtMaxSplit) return cudaErrorInvalidValue;

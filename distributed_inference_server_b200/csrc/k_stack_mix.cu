@@ -13,7 +13,9 @@ __device__ __forceinline__ float silu_(float v) { return v / (1.f + expf(-v)); }
 // in warp order, so the sum's order is fixed.  A span that starts at position 0 starts from S = 0 (the slot is not read).
 // GATE false: one decay per head, q, k, v through SiLU.  GATE true: the decay is a vector per token (dec [T][H*d], one factor per
 // row of S), q is multiplied by qscale, no activation.
-struct LightCols { int q, k, v; };  // first column of head 0's q, k, v in a row of proj
+// first column of head 0's q, k, v in a row of proj.  hpg > 1: q and k are shared by groups of hpg consecutive heads (head h reads
+// block h / hpg).  dec_head (gated form): the decay is one factor per token and head, dec [T][H], not one per key channel.
+struct LightCols { int q, k, v; int hpg = 1; int dec_head = 0; };
 template <bool GATE>
 __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj, long long ld, LightCols col, const float *decay,
                                                               const float *dec, float qscale, float *state, StackSpans sp, float *o, int H,
@@ -35,10 +37,10 @@ __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj,
     const float *row = proj + (long long)(tok0 + t) * ld;
     __syncthreads();
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      const float qv = row[col.q + (long long)h * d + i], kv = row[col.k + (long long)h * d + i];
+      const float qv = row[col.q + (long long)(h / col.hpg) * d + i], kv = row[col.k + (long long)(h / col.hpg) * d + i];
       qs[i] = GATE ? qv * qscale : silu_(qv);
       ks[i] = GATE ? kv : silu_(kv);
-      if (GATE) as[i] = dec[(long long)(tok0 + t) * H * d + (long long)h * d + i];
+      if (GATE) as[i] = col.dec_head ? dec[(long long)(tok0 + t) * H + h] : dec[(long long)(tok0 + t) * H * d + (long long)h * d + i];
     }
     for (int j = threadIdx.x; j < dv; j += blockDim.x) {
       const float vv = row[col.v + (long long)h * dv + j];
@@ -137,10 +139,14 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
   for (int u = 0; u < 2; u++) {
     const int c = threadIdx.x + u * 256;
     src[u] = nullptr; sstride[u] = ld; sdst[u] = qs; dstride[u] = DP; mul[u] = 1.f;
-    if (c < d) { src[u] = proj + col.q + (long long)h * d + c; sdst[u] = qs + c; mul[u] = GATE ? qscale : 1.f; }
-    else if (c < 2 * d) { src[u] = proj + col.k + (long long)h * d + (c - d); sdst[u] = ks + (c - d); }
+    if (c < d) { src[u] = proj + col.q + (long long)(h / col.hpg) * d + c; sdst[u] = qs + c; mul[u] = GATE ? qscale : 1.f; }
+    else if (c < 2 * d) { src[u] = proj + col.k + (long long)(h / col.hpg) * d + (c - d); sdst[u] = ks + (c - d); }
     else if (c < 2 * d + dv) { src[u] = proj + col.v + (long long)h * dv + (c - 2 * d); sdst[u] = vs + (c - 2 * d); dstride[u] = DVP; }
-    else if (c < per) { src[u] = dec + (long long)h * d + (c - 2 * d - dv); sstride[u] = (long long)H * d; sdst[u] = as + (c - 2 * d - dv); }
+    else if (c < per) {  // one decay per key channel, or the head's one decay copied to every channel
+      src[u] = col.dec_head ? dec + h : dec + (long long)h * d + (c - 2 * d - dv);
+      sstride[u] = col.dec_head ? (long long)H : (long long)H * d;
+      sdst[u] = as + (c - 2 * d - dv);
+    }
   }
   float tmp[2 * kLightTok];
   auto fetch = [&](int t0) {
@@ -375,6 +381,131 @@ cudaError_t launch_stack_gla(const float *proj, long long ld, int q_off, int k_o
   static DeviceOnce once;
   DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_lightning_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); }));
   stack_lightning_kernel<true><<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ state-space mixer
+// The recurrence S = a_t S + B_t (dt_t x_t)^T, o_t = S^T C_t is the gated one above with a decay per token and head, keys B and
+// queries C shared by the heads of a group, and values dt x: the same kernels, their staging told where to read.
+cudaError_t launch_stack_ssd(const float *buf, long long ld_b, int c_off, int b_off, int v_off, int hpg, const float *dec, float *state,
+                             const StackSpans &sp, float *o, int H, int N, int P, float *seg, float *seg_a, int max_len, cudaStream_t st) {
+  LightCols col{c_off, b_off, v_off};
+  col.hpg = hpg < 1 ? 1 : hpg;
+  col.dec_head = 1;
+  const int d = N, dv = P;
+  if (d <= 32 && dv <= 64) return lightning_reg<4, 2, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 64 && dv <= 64) return lightning_reg<8, 2, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 64 && dv <= 128) return lightning_reg<8, 4, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 128 && dv <= 128) return lightning_reg<16, 4, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  const int threads = 256;
+  const size_t sh = ((size_t)d * dv + 3 * d + dv + (size_t)(threads / 32) * dv) * sizeof(float);
+  if (sh > 220 * 1024) return cudaErrorInvalidValue;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_lightning_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); }));
+  stack_lightning_kernel<true><<<dim3(sp.n_spans, H), threads, sh, st>>>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv);
+  return cudaGetLastError();
+}
+
+// Convolution, SiLU, step sizes and decays; one block per token.  The input at position p of the sequence comes from the span's
+// own rows of proj or, before the span's start, from the slot's tail (tail[i] holds position pos0 - (taps-1) + i); before the
+// sequence's start it is zero, so a slot that another sequence used before needs no clearing.
+constexpr int kConvMaxTaps = 16;
+__global__ void __launch_bounds__(256) stack_ssm_conv_kernel(const float *__restrict__ proj, long long ld, int x_off, int dt_off, int C,
+                                                             int H, int P, int taps, const float *__restrict__ cw,
+                                                             const float *__restrict__ cb, const float *__restrict__ vec,
+                                                             const float *__restrict__ cstate, StackSpans sp, float *__restrict__ buf,
+                                                             long long ld_b, float *__restrict__ dec) {
+  extern __shared__ float dts[];  // [H]
+  const int t = blockIdx.x;
+  const int s = sp.span[t], tok0 = sp.sp_tok0[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  const int back_in_span = t - tok0;  // tokens of the span in front of t
+  const float *row = proj + (long long)t * ld;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float z = row[dt_off + h] + vec[h];
+    const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));  // softplus, no clamp
+    dts[h] = dt;
+    dec[(long long)t * H + h] = expf(-expf(vec[H + h]) * dt);
+  }
+  __syncthreads();
+  const float *tail = cstate + (long long)slot * (taps - 1) * C;
+  const int inner = H * P;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = cb[c];
+    for (int j = 0; j < taps; j++) {
+      const int back = taps - 1 - j;
+      float v;
+      if (back <= back_in_span) v = row[x_off + c - (long long)back * ld];
+      else v = (pos0 + back_in_span - back >= 0) ? tail[(long long)((taps - 1) - (back - back_in_span)) * C + c] : 0.f;
+      acc = fmaf(cw[(long long)c * taps + j], v, acc);
+    }
+    const float a = silu_(acc);
+    buf[(long long)t * ld_b + c] = a;
+    if (c < inner) buf[(long long)t * ld_b + C + c] = a * dts[c / P];
+  }
+}
+// The tail moves on to the span's last taps - 1 inputs (a span shorter than that keeps the end of the old tail in front).
+__global__ void stack_ssm_tail_kernel(const float *__restrict__ proj, long long ld, int x_off, float *cstate, StackSpans sp, int C,
+                                      int taps) {
+  const int s = blockIdx.x;
+  const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  float *tail = cstate + (long long)slot * (taps - 1) * C;
+  const int n = taps - 1;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    float nv[kConvMaxTaps];
+    for (int k = 0; k < n; k++) {
+      const int rel = len - n + k;  // index relative to the span's first token of the position tail'[k] holds
+      if (rel >= 0) nv[k] = proj[(long long)(tok0 + rel) * ld + x_off + c];
+      else nv[k] = (pos0 + rel >= 0) ? tail[(long long)(n + rel) * C + c] : 0.f;
+    }
+    for (int k = 0; k < n; k++) tail[(long long)k * C + c] = nv[k];
+  }
+}
+cudaError_t launch_stack_ssm_conv(const float *proj, long long ld, int x_off, int dt_off, int C, int H, int P, int taps, const float *cw,
+                                  const float *cb, const float *vec, float *cstate, const StackSpans &sp, float *buf, long long ld_b,
+                                  float *dec, cudaStream_t st) {
+  if (taps < 1 || taps > kConvMaxTaps || (size_t)H * 4 > 40 * 1024) return cudaErrorInvalidValue;
+  if (sp.T <= 0) return cudaSuccess;
+  stack_ssm_conv_kernel<<<sp.T, 256, (size_t)H * sizeof(float), st>>>(proj, ld, x_off, dt_off, C, H, P, taps, cw, cb, vec, cstate, sp, buf, ld_b, dec);
+  if (taps > 1) stack_ssm_tail_kernel<<<dim3(sp.n_spans, (C + 1023) / 1024), 256, 0, st>>>(proj, ld, x_off, cstate, sp, C, taps);
+  return cudaGetLastError();
+}
+
+// y = (o + D[h] x) silu(z), then each of `parts` equal stretches of the row is divided by its own root mean square, times w.
+// One block per token, the row in shared memory.
+template <bool F32>
+__global__ void __launch_bounds__(256) stack_ssm_out_kernel(const float *__restrict__ o, const float *__restrict__ buf, long long ld_b,
+                                                            const float *__restrict__ z, long long ld, const float *__restrict__ D,
+                                                            const float *__restrict__ w, int parts, void *__restrict__ out, int H, int P,
+                                                            float eps) {
+  extern __shared__ float yrow[];  // [H*P]
+  __shared__ float sh[32];
+  const long long t = blockIdx.x;
+  const int inner = H * P, per = inner / parts;
+  for (int i = threadIdx.x; i < inner; i += blockDim.x) {
+    const float y = fmaf(D[i / P], buf[t * ld_b + i], o[t * inner + i]);
+    yrow[i] = y * silu_(z[t * ld + i]);
+  }
+  __syncthreads();
+  for (int g = 0; g < parts; g++) {
+    float q = 0.f;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) { const float v = yrow[g * per + i]; q += v * v; }
+    const float r = rsqrtf(block_sum(q, sh) / (float)per + eps);
+    for (int i = threadIdx.x; i < per; i += blockDim.x) st_el<F32>(out, t * inner + g * per + i, yrow[g * per + i] * r * w[g * per + i]);
+  }
+}
+cudaError_t launch_stack_ssm_out(const float *o, const float *buf, long long ld_b, const float *z, long long ld, const float *D,
+                                 const float *w, int parts, void *out, bool f32, int T, int H, int P, float eps, cudaStream_t st) {
+  const int inner = H * P;
+  if (parts < 1 || inner % parts || (size_t)inner * 4 > 160 * 1024) return cudaErrorInvalidValue;
+  if (T <= 0) return cudaSuccess;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(stack_ssm_out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_ssm_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  }));
+  const size_t shb = (size_t)inner * 4;
+  if (f32) stack_ssm_out_kernel<true><<<T, 256, shb, st>>>(o, buf, ld_b, z, ld, D, w, parts, out, H, P, eps);
+  else stack_ssm_out_kernel<false><<<T, 256, shb, st>>>(o, buf, ld_b, z, ld, D, w, parts, out, H, P, eps);
   return cudaGetLastError();
 }
 

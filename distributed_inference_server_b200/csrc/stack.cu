@@ -158,7 +158,10 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       if ((fl & DIS_ATTN_SINK) && (fl & DIS_ATTN_SIGMOID)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "a sink belongs to softmax weights");
       if ((fl & DIS_ATTN_QK_NORM) && (fl & DIS_ATTN_QK_NORM_HEAD)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "query/key norm: whole projection or per head, not both");
       if ((fl & DIS_ATTN_BIAS) && (fl & DIS_ATTN_BIAS_QKV)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "biases: q, k, o or q, k, v, not both");
-      if (lc.mask_chunk < 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "mask_chunk must not be negative");
+      if (lc.mask_chunk < 0 || lc.mask_window < 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "mask_chunk and mask_window must not be negative");
+      if (!(lc.score_softcap >= 0.f)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "score_softcap must not be negative");
+      if ((fl & DIS_ATTN_SIGMOID) && (lc.score_softcap > 0.f || (fl & DIS_ATTN_SINK_UNIT))) return fail(DIS_ERR_INVALID_ARGUMENT, at + "a score soft cap and a sink belong to softmax weights");
+      if ((fl & DIS_ATTN_SINK) && (fl & DIS_ATTN_SINK_UNIT)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "sink: a learned logit per head or the unit term, not both");
       if (lc.kv_from >= 0) {
         if (lc.kv_from >= i) return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_from must name an earlier layer");
         const dis_layer_config &src = M.layers[(size_t)lc.kv_from].c;
@@ -168,7 +171,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
           return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_from must name an attention layer with a cache of its own and the same kv_heads, dim, vdim and rotation");
       }
       const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
-      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, sc->norm_eps, lc.mask_chunk};
+      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, sc->norm_eps, lc.mask_chunk, lc.mask_window, lc.score_softcap};
       const int bq = stack_attn_block_tokens(sa, sc->compute_dtype == DIS_F32);
       if (((size_t)32 * (d + dv + 10) + (size_t)(H / G) * (d + dv + 2)) * 4 > 200 * 1024) return fail(DIS_ERR_INVALID_ARGUMENT, at + "dim + vdim does not fit shared memory");
       stack_abq = stack_abq ? std::min(stack_abq, bq) : bq;
@@ -191,13 +194,27 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         L.n_in = L.ga_off + lc.gla_rank;
         L.n_act += Hr * dvr;
       }
+    } else if (lc.mixer == DIS_MIX_SSM) {
+      if (L.c.ssm_norm_groups == 0) L.c.ssm_norm_groups = 1;
+      const int H = lc.heads, P = lc.vdim, N = lc.ssm_state, G = lc.ssm_groups;
+      if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G || lc.conv_taps < 1 || lc.conv_taps > 16 || L.c.ssm_norm_groups < 1 ||
+          (H * P) % L.c.ssm_norm_groups)
+        return fail(DIS_ERR_INVALID_ARGUMENT, at + "the state-space mixer needs heads (a multiple of ssm_groups), vdim, ssm_state, conv_taps 1..16 and ssm_norm_groups dividing heads * vdim");
+      if ((N > 128 || P > 128) && ((size_t)N * P + 3 * N + 9 * P) * 4 > 220 * 1024)
+        return fail(DIS_ERR_INVALID_ARGUMENT, at + "state-space mixer: ssm_state * vdim does not fit shared memory");
+      if ((size_t)H * P * 4 > 160 * 1024) return fail(DIS_ERR_INVALID_ARGUMENT, at + "state-space mixer: heads * vdim above 40960");
+      // rows of the input projection: z | x | B | C | dt; the convolution runs over x | B | C
+      L.conv_ch = H * P + 2 * G * N;
+      L.x_off = H * P; L.dt_off = L.x_off + L.conv_ch;
+      L.n_in = L.dt_off + H;
     } else return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown mixer");
-    if (lc.mlp_act != DIS_ACT_CLAMPED && lc.mlp_act != DIS_ACT_GELU_TANH && lc.mlp_act != DIS_ACT_SILU) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown feed-forward activation");
+    if (lc.mlp_act != DIS_ACT_CLAMPED && lc.mlp_act != DIS_ACT_GELU_TANH && lc.mlp_act != DIS_ACT_SILU && lc.mlp_act != DIS_ACT_RELU2) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown feed-forward activation");
+    L.gu_rows = lc.mlp_act == DIS_ACT_RELU2 ? 1 : 2;
     if (lc.mlp == DIS_MLP_DENSE) { if (lc.ff <= 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "ff"); }
     else if (lc.mlp == DIS_MLP_MOE) {
       if (lc.ff <= 0 || lc.experts <= 0 || lc.top <= 0 || lc.top > lc.experts || lc.top > 32 || lc.experts > 1024)
         return fail(DIS_ERR_INVALID_ARGUMENT, at + "experts: 1 <= top <= min(experts, 32), experts <= 1024");
-      if (lc.route_kind != DIS_ROUTE_SOFTMAX_TOP && lc.route_kind != DIS_ROUTE_SIGMOID_GROUPS) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown router kind");
+      if (lc.route_kind != DIS_ROUTE_SOFTMAX_TOP && lc.route_kind != DIS_ROUTE_SIGMOID_GROUPS && lc.route_kind != DIS_ROUTE_SOFTMAX_ALL) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown router kind");
       if (lc.route_groups > 1) {
         if (lc.route_kind != DIS_ROUTE_SIGMOID_GROUPS || lc.experts % lc.route_groups || lc.route_keep < 1 || lc.route_keep > lc.route_groups ||
             lc.route_keep * (lc.experts / lc.route_groups) < lc.top)
@@ -208,6 +225,13 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   }
   if (sc->norm_kind != DIS_NORM_RMS_SCALAR && sc->norm_kind != DIS_NORM_LAYER && sc->norm_kind != DIS_NORM_RMS) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: norm_kind");
   if (sc->logit_softcap < 0.f) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: logit_softcap must not be negative");
+  const bool pre_frame = (sc->frame_flags & DIS_FRAME_PRE_NORM) != 0;
+  if (pre_frame && (sc->norm_kind != DIS_NORM_RMS || sc->canon_taps != 0))
+    return fail(DIS_ERR_INVALID_ARGUMENT, "stack: the pre-norm frame is built for RMS norms with gain vectors and no input convolution");
+  if (sc->streams < 0 || sc->streams > 8 || (sc->streams > 0 && !pre_frame))
+    return fail(DIS_ERR_INVALID_ARGUMENT, "stack: residual streams (at most 8) need the pre-norm frame");
+  const bool loop_proj = sc->loop_times > 0 && !(sc->frame_flags & DIS_FRAME_LOOP_PLAIN);
+  const int n_streams = std::max(1, sc->streams);
   if (sc->loop_times < 0 || (sc->loop_times > 0 && !(0 <= sc->loop_start && sc->loop_start < sc->loop_stop && sc->loop_stop <= sc->n_layers)))
     return fail(DIS_ERR_INVALID_ARGUMENT, "stack: a loop needs 0 <= loop_start < loop_stop <= n_layers");
   if (M.c.embed_scale == 0.f) M.c.embed_scale = 1.f;
@@ -262,9 +286,12 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   };
   // ---- weights
   ENG_CUDA(tensor(M.embed, (size_t)sc->vocab * W, M.f32));
-  ENG_CUDA(tensor(M.head, (size_t)sc->vocab * W, M.f32));
   name("embed", &M.embed, 0, {sc->vocab, W}, -1);
-  name("head", &M.head, 0, {sc->vocab, W}, -1);
+  if (sc->frame_flags & DIS_FRAME_TIED_HEAD) M.head = M.embed;  // the same memory: logits are products with the embedding rows
+  else {
+    ENG_CUDA(tensor(M.head, (size_t)sc->vocab * W, M.f32));
+    name("head", &M.head, 0, {sc->vocab, W}, -1);
+  }
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.final_g), 4));
   const bool ln = sc->norm_kind == DIS_NORM_LAYER || sc->norm_kind == DIS_NORM_RMS;  // norms with vectors
   const bool ln_bias = sc->norm_kind == DIS_NORM_LAYER;
@@ -276,7 +303,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       name("final.norm.b", &M.final_b, 0, {W}, -1);
     }
   }
-  if (sc->loop_times > 0) {
+  if (loop_proj) {
     ENG_CUDA(tensor(M.loop_in, (size_t)W * 2 * W, M.f32));
     ENG_CUDA(tensor(M.loop_step, (size_t)sc->loop_times * W, true));
     name("loop.in", &M.loop_in, 0, {W, 2 * W}, -1);
@@ -284,7 +311,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   }
   static StackTensor dummy;  // scalars are written through their own small tensors below
   (void)dummy;
-  size_t max_proj = 1, max_mix = 1, max_act = 1, max_qf = 1, max_vrot = 0, max_dec = 0;
+  size_t max_proj = 1, max_mix = 1, max_act = 1, max_qf = 1, max_vrot = 0, max_dec = 0, max_ssm = 0;
   int max_top = 0, max_e = 0;
   bool any_shared = false;
   size_t max_sff = 0;
@@ -303,12 +330,21 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       const char *gn[4] = {"norm1", "norm1b", "norm2", "norm2b"};
       for (int k = 0; k < 4; k++) {
         if (k >= 2 && lc.mlp == DIS_MLP_NONE) continue;
+        if (pre_frame && (k & 1)) continue;  // no norms behind the sublayers
         ENG_CUDA(tensor(L.ln_w[k], (size_t)W, true));
         name(pre + gn[k], &L.ln_w[k], 0, {W}, i);
         if (!ln_bias) continue;
         ENG_CUDA(tensor(L.ln_b[k], (size_t)W, true));
         name(pre + gn[k] + ".b", &L.ln_b[k], 0, {W}, i);
       }
+    }
+    for (int q = 0; q < (lc.mlp == DIS_MLP_NONE ? 1 : 2) && sc->streams > 0; q++) {  // coefficients of the residual streams
+      const int S = sc->streams;
+      const std::string hp = pre + "hc" + std::to_string(q + 1) + ".";
+      ENG_CUDA(tensor(L.hc[q], (size_t)(2 * S + S * S), true));
+      name(hp + "in", &L.hc[q], 0, {S}, i);
+      name(hp + "out", &L.hc[q], (size_t)S, {S}, i);
+      name(hp + "mix", &L.hc[q], (size_t)2 * S, {S, S}, i);
     }
     ENG_CUDA(tensor(L.w_in, (size_t)L.n_in * W, M.f32));
     max_proj = std::max(max_proj, (size_t)L.n_in);
@@ -363,6 +399,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         ENG_CUDA(tensor(L.sink, (size_t)H, true));
         name(a + "sink", &L.sink, 0, {H}, i);
       }
+      if (lc.attn_flags & DIS_ATTN_SINK_UNIT) ENG_CUDA(tensor(L.sink, (size_t)H, true));  // zero logits: the denominator's extra 1
       if (lc.attn_flags & DIS_ATTN_QK_NORM) {
         ENG_CUDA(tensor(L.qk_norm, (size_t)(H + G) * d, true));
         name(a + "q.norm", &L.qk_norm, 0, {H * d}, i);
@@ -418,6 +455,25 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         max_dec = std::max(max_dec, (size_t)Hr * dr);
       }
       max_act = std::max(max_act, (size_t)L.n_act);
+    } else if (lc.mixer == DIS_MIX_SSM) {
+      const int H = lc.heads, P = lc.vdim, C = L.conv_ch, inner = H * P;
+      name(pre + "mix.in", &L.w_in, 0, {L.n_in, W}, i);
+      ENG_CUDA(tensor(L.conv_w, (size_t)C * lc.conv_taps, true));
+      name(pre + "mix.conv", &L.conv_w, 0, {C, lc.conv_taps}, i);
+      ENG_CUDA(tensor(L.conv_b, (size_t)C, true));
+      name(pre + "mix.conv.b", &L.conv_b, 0, {C}, i);
+      ENG_CUDA(tensor(L.ssm_vec, (size_t)3 * H, true));
+      name(pre + "mix.dt_bias", &L.ssm_vec, 0, {H}, i);
+      name(pre + "mix.A_log", &L.ssm_vec, (size_t)H, {H}, i);
+      name(pre + "mix.D", &L.ssm_vec, (size_t)2 * H, {H}, i);
+      ENG_CUDA(tensor(L.norm_w, (size_t)inner, true));
+      name(pre + "mix.norm", &L.norm_w, 0, {inner}, i);
+      ENG_CUDA(tensor(L.w_o, (size_t)W * inner, M.f32));
+      name(pre + "mix.o", &L.w_o, 0, {W, inner}, i);
+      max_mix = std::max(max_mix, (size_t)inner);
+      max_act = std::max(max_act, (size_t)inner);
+      max_ssm = std::max(max_ssm, (size_t)C + inner);
+      max_dec = std::max(max_dec, (size_t)H);
     } else if (lc.mixer == DIS_MIX_MINGRU) {
       const int n = lc.width;
       name(pre + "mix.z", &L.w_in, 0, {n, W}, i);
@@ -453,11 +509,11 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       stack_lat_heads = std::max(stack_lat_heads, H);
     }
     if (lc.mlp == DIS_MLP_DENSE) {
-      const int ff = lc.ff;
-      ENG_CUDA(tensor(L.w_gu, (size_t)2 * ff * W, M.f32));
+      const int ff = lc.ff, gr = L.gu_rows;
+      ENG_CUDA(tensor(L.w_gu, (size_t)gr * ff * W, M.f32));
       ENG_CUDA(tensor(L.w_down, (size_t)W * ff, M.f32));
-      name(pre + "mlp.gate", &L.w_gu, 0, {ff, W}, i);
-      name(pre + "mlp.up", &L.w_gu, (size_t)ff * W, {ff, W}, i);
+      if (gr == 2) name(pre + "mlp.gate", &L.w_gu, 0, {ff, W}, i);
+      name(pre + "mlp.up", &L.w_gu, (size_t)(gr - 1) * ff * W, {ff, W}, i);
       name(pre + "mlp.down", &L.w_down, 0, {W, ff}, i);
       if (lc.mlp_act == DIS_ACT_CLAMPED) {  // the clamped unit carries biases, the gelu unit none
         ENG_CUDA(tensor(L.b_gu, (size_t)2 * ff, true));
@@ -466,13 +522,14 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         name(pre + "mlp.up.b", &L.b_gu, (size_t)ff, {ff}, i);
         name(pre + "mlp.down.b", &L.b_down, 0, {W}, i);
       }
-      max_proj = std::max(max_proj, (size_t)2 * ff);
+      max_proj = std::max(max_proj, (size_t)gr * ff);
       max_act = std::max(max_act, (size_t)ff);
     } else if (lc.mlp == DIS_MLP_MOE) {
-      const int ff = lc.ff, E = lc.experts;
-      ENG_CUDA(tensor(L.w_gu, (size_t)E * 2 * ff * W, M.f32));
+      const int ff = lc.ff, E = lc.experts, gr = L.gu_rows;
+      const bool shared_gate = lc.shared_ff > 0 && !(lc.mlp_flags & DIS_MLP_SHARED_PLAIN);
+      ENG_CUDA(tensor(L.w_gu, (size_t)E * gr * ff * W, M.f32));
       ENG_CUDA(tensor(L.w_down, (size_t)E * W * ff, M.f32));
-      ENG_CUDA(tensor(L.router, (size_t)(E + (lc.shared_ff > 0 ? 1 : 0)) * W, true));
+      ENG_CUDA(tensor(L.router, (size_t)(E + (shared_gate ? 1 : 0)) * W, true));
       name(pre + "mlp.router", &L.router, 0, {E, W}, i);
       if (lc.route_kind == DIS_ROUTE_SIGMOID_GROUPS) {
         ENG_CUDA(tensor(L.correction, (size_t)E, true));
@@ -480,24 +537,24 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       }
       if (lc.shared_ff > 0) {  // the shared expert: a dense unit of its own size; the logit of its gate is one more router row
         const int sf = lc.shared_ff;
-        ENG_CUDA(tensor(L.w_sgu, (size_t)2 * sf * W, M.f32));
+        ENG_CUDA(tensor(L.w_sgu, (size_t)gr * sf * W, M.f32));
         ENG_CUDA(tensor(L.w_sdown, (size_t)W * sf, M.f32));
-        name(pre + "mlp.shared.gate", &L.w_sgu, 0, {sf, W}, i);
-        name(pre + "mlp.shared.up", &L.w_sgu, (size_t)sf * W, {sf, W}, i);
+        if (gr == 2) name(pre + "mlp.shared.gate", &L.w_sgu, 0, {sf, W}, i);
+        name(pre + "mlp.shared.up", &L.w_sgu, (size_t)(gr - 1) * sf * W, {sf, W}, i);
         name(pre + "mlp.shared.down", &L.w_sdown, 0, {W, sf}, i);
-        name(pre + "mlp.shared.sg", &L.router, (size_t)E * W, {1, W}, i);
-        max_proj = std::max(max_proj, (size_t)2 * sf);
+        if (shared_gate) name(pre + "mlp.shared.sg", &L.router, (size_t)E * W, {1, W}, i);
+        max_proj = std::max(max_proj, (size_t)gr * sf);
         max_act = std::max(max_act, (size_t)sf);
         max_sff = std::max(max_sff, (size_t)sf);
         any_shared = true;
       }
       for (int e = 0; e < E; e++) {
         const std::string ep = pre + "mlp.e" + std::to_string(e) + ".";
-        name(ep + "gate", &L.w_gu, (size_t)e * 2 * ff * W, {ff, W}, i);
-        name(ep + "up", &L.w_gu, ((size_t)e * 2 * ff + ff) * W, {ff, W}, i);
+        if (gr == 2) name(ep + "gate", &L.w_gu, (size_t)e * 2 * ff * W, {ff, W}, i);
+        name(ep + "up", &L.w_gu, ((size_t)e * gr * ff + (size_t)(gr - 1) * ff) * W, {ff, W}, i);
         name(ep + "down", &L.w_down, (size_t)e * W * ff, {W, ff}, i);
       }
-      max_proj = std::max(max_proj, (size_t)lc.top * 2 * ff);
+      max_proj = std::max(max_proj, (size_t)lc.top * gr * ff);
       max_act = std::max(max_act, (size_t)lc.top * ff);
       max_top = std::max(max_top, lc.top);
       max_e = std::max(max_e, E);
@@ -545,11 +602,23 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     if (lc.mixer == DIS_MIX_LIGHTNING) ENG_CUDA(alloc(reinterpret_cast<void **>(&R.state), slots * lc.heads * lc.dim * lc.vdim * 4));
     else if (lc.mixer == DIS_MIX_MINGRU) ENG_CUDA(alloc(reinterpret_cast<void **>(&R.state), slots * lc.width * 4));
     else if (lc.mixer == DIS_MIX_PARALLEL) ENG_CUDA(alloc(reinterpret_cast<void **>(&R.state), slots * lc.gla_heads * lc.gla_dim * lc.gla_vdim * 4));
+    else if (lc.mixer == DIS_MIX_SSM) {
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&R.state), slots * lc.heads * lc.ssm_state * lc.vdim * 4));
+      if (lc.conv_taps > 1) ENG_CUDA(alloc(reinterpret_cast<void **>(&R.conv_state), slots * (lc.conv_taps - 1) * M.layers[(size_t)R.layer].conv_ch * 4));
+    }
   }
   M.views.assign(scalars.begin(), scalars.end());
   // ---- activations
   const size_t cap = (size_t)cap_tokens;
-  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.x), cap * W * 4));
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.x), cap * n_streams * W * 4));
+  if (sc->frame_flags & DIS_FRAME_POS_SINUS) {  // frequencies of the position vector, formed in double
+    const double base = sc->pos_base > 0.f ? (double)sc->pos_base : 10000.0;
+    std::vector<double> f((size_t)(W + 1) / 2);
+    for (size_t k = 0; k < f.size(); k++) f[k] = std::pow(base, -2.0 * (double)k / (double)W);
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.pos_freq), f.size() * 8));
+    ENG_CUDA(cudaMemcpy(M.pos_freq, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
+  }
+  if (max_ssm) { M.ssm_ld = max_ssm; ENG_CUDA(alloc(reinterpret_cast<void **>(&M.ssm), cap * max_ssm * 4)); }
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.y), cap * W * 4));
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.hn), cap * W * 4));
   ENG_CUDA(alloc(&M.hc, cap * W * esz));
@@ -559,7 +628,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.qf), cap * max_qf * 4));
   ENG_CUDA(alloc(&M.act, cap * max_act * esz));
   ENG_CUDA(alloc(&M.xr, (size_t)M.max_rows * W * esz));
-  if (sc->loop_times > 0) {
+  if (loop_proj) {
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.x0), cap * W * 4));
     ENG_CUDA(alloc(&M.xcat, cap * 2 * W * esz));
   }
@@ -598,6 +667,10 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       if (L.c.mixer == DIS_MIX_PARALLEL) {
         seg = std::max(seg, stack_lightning_seg_floats(cap_tokens, max_batch, L.c.gla_heads, L.c.gla_dim, L.c.gla_vdim));
         seg_a = std::max(seg_a, stack_lightning_seg_decay_floats(cap_tokens, max_batch, L.c.gla_heads, L.c.gla_dim));
+      }
+      if (L.c.mixer == DIS_MIX_SSM && L.c.ssm_state <= 128 && L.c.vdim <= 128) {
+        seg = std::max(seg, stack_lightning_seg_floats(cap_tokens, max_batch, L.c.heads, L.c.ssm_state, L.c.vdim));
+        seg_a = std::max(seg_a, stack_lightning_seg_decay_floats(cap_tokens, max_batch, L.c.heads, L.c.ssm_state));
       }
     }
     if (const char *g = getenv("DIS_STACK_LIGHT_SEGMENTS")) seg = atoi(g) != 0 ? seg : 0;
@@ -903,8 +976,11 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
     stack_att_plan.assign(M.layers.size(), whole);
     for (size_t li = 0; li < M.layers.size(); li++) {
       const dis_layer_config &lc = M.layers[li].c;
-      if ((lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) && lc.mask_chunk > 0)
-        stack_att_plan[li] = att_slices((int)std::min<long long>(stack_max_ctx, (long long)lc.mask_chunk + stack_abq));
+      if (!(lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL)) continue;
+      long long bound = stack_max_ctx;  // keys a query block can reach at most
+      if (lc.mask_chunk > 0) bound = std::min(bound, (long long)lc.mask_chunk + stack_abq);
+      if (lc.mask_window > 0) bound = std::min(bound, (long long)lc.mask_window + stack_abq);
+      if (bound < stack_max_ctx) stack_att_plan[li] = att_slices((int)bound);
     }
   }
   // A pass of single tokens only (decode rows, no kept prompt positions) has the same launches whenever its size, its
@@ -1051,14 +1127,25 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     kl++;
     return launch_stack_gemm(g, cur_st);
   };
-  RET_CUDA(launch_stack_embed(M.embed.ptr, f32, sp.tokens, M.x, M.x0, M.c.embed_scale, T, W, stream)); kl++;
+  const bool pre_frame = (M.c.frame_flags & DIS_FRAME_PRE_NORM) != 0;  // x += f(norm(x)), over residual streams where the model has them
+  const int n_streams = std::max(1, M.c.streams);
+  RET_CUDA(launch_stack_embed(M.embed.ptr, f32, sp.tokens, sp.pos, M.pos_freq, M.x, M.x0, M.c.embed_scale, T, W, n_streams, stream)); kl++;
   const float *pend_y = nullptr, *pend_post = nullptr, *pend_post_b = nullptr;
+  const float *pend_hc = nullptr, *next_hc = nullptr;  // stream coefficients of the sublayer whose product is pending / of the coming one
   const bool ln = M.c.norm_kind == DIS_NORM_LAYER || M.c.norm_kind == DIS_NORM_RMS;  // norms with vectors: one boundary kernel
   const bool rms = M.c.norm_kind == DIS_NORM_RMS;
   const bool single = T == n_spans;  // every span one token long: the fused boundary kernel
   // The boundary in front of a sublayer: the product before it joins the residual through its post norm, then the pre norm (and
   // the convolution) makes the sublayer's input.  pre == null: only the residual is updated.  cat: [x ; x0] is written too.
   auto sublayer_in = [&](const float *pre, const float *pre_b, const float *cw, float *cstate, bool cat = false) -> cudaError_t {
+    if (pre_frame) {  // one kernel: the pending product joins the stream(s), the coming sublayer's input is read off and normed
+      kl++;
+      const float *src = pend_y ? (pend_parts > 1 || pend_bias ? pend_src : pend_y) : nullptr;
+      const cudaError_t e = launch_stack_boundary_hc(M.x, n_streams, src, pend_parts, pend_stride, pend_bias, pend_hc, next_hc, pre, M.hc, f32, T,
+                                                     W, eps, stream);
+      pend_y = nullptr; pend_parts = 1; pend_bias = nullptr; pend_hc = nullptr;
+      return e;
+    }
     if (ln) {  // layer norms: one kernel for passes of any shape; it sums the slices of the product before and adds its bias
       kl++;
       const float *src = pend_y ? (pend_parts > 1 || pend_bias ? pend_src : pend_y) : nullptr;
@@ -1106,6 +1193,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   // may stay unsummed for the next boundary kernel (out is then M.y, as the caller expects).
   auto dense_ff = [&](const StackTensor &w_gu, const StackTensor &b_gu, const StackTensor &w_down, const StackTensor &b_down, int ff,
                       int act_kind, float limit, float *out, bool later_ok) -> cudaError_t {
+    const int gu_rows = act_kind == DIS_ACT_RELU2 ? 1 : 2;  // an ungated unit has no gate rows
     // bf16, a unit without biases (gelu_tanh or SiLU gate), prompt-sized passes: gate and up run as one tensor-core product with
     // two accumulators whose epilogue writes act(gate) * up (the product the Llama path uses with SiLU).  Decode-sized passes
     // keep the split-K product below, whose slices the gated unit sums: at these widths a single pass over K leaves each CTA a
@@ -1130,7 +1218,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     }
     // the gated unit sums the slices of its input product itself and adds the bias the product left out
     const float *gu_bias = nullptr;
-    RET_CUDA(gemm(M.hc, f32, W, w_gu, 0, reinterpret_cast<const float *>(b_gu.ptr), cur_proj, T, 2 * ff, W, cap_tokens, &gu_bias, true));
+    RET_CUDA(gemm(M.hc, f32, W, w_gu, 0, reinterpret_cast<const float *>(b_gu.ptr), cur_proj, T, gu_rows * ff, W, cap_tokens, &gu_bias, true));
     const bool sliced = pend_parts > 1 || pend_bias;
     RET_CUDA(launch_stack_glu(sliced ? pend_src : cur_proj, sliced ? pend_parts : 1, pend_stride, sliced ? pend_bias : gu_bias, cur_act, f32, nullptr,
                               T, ff, limit, act_kind, cur_st));
@@ -1142,13 +1230,14 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     StackRun &Rn = M.runs[ri];
     StackLayer &L = M.layers[(size_t)Rn.layer];
     const dis_layer_config &lc = L.c;
-    if (Rn.loop_pass >= 0) {
+    if (Rn.loop_pass >= 0 && !(M.c.frame_flags & DIS_FRAME_LOOP_PLAIN)) {
       // in front of a loop pass: x = loop_in [x ; x0] + loop_step[pass].  The boundary kernel adds the product before to the
       // residual and writes [x ; x0]; the projection's result (with the pass's vector as its bias) replaces the residual.
       RET_CUDA(sublayer_in(nullptr, nullptr, nullptr, nullptr, true));
       RET_CUDA(gemm(M.xcat, f32, 2 * W, M.loop_in, 0, reinterpret_cast<const float *>(M.loop_step.ptr) + (size_t)Rn.loop_pass * W, M.x, T, W,
                     2 * W, cap_tokens));
     }
+    next_hc = reinterpret_cast<const float *>(L.hc[0].ptr);
     RET_CUDA(sublayer_in(norm_w(L, 0), norm_b(L, 0), L.canon1, Rn.cstate1));
     const int N = L.n_in;
     const float *in_bias = nullptr;  // minGRU adds its projections' biases itself when the product left them out
@@ -1175,6 +1264,21 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       RET_CUDA(launch_stack_norm_gate(M.mix, reinterpret_cast<const float *>(L.norm_w.ptr), M.proj + L.g_off, N, M.act, f32, T, H * dv, eps, stream));
       kl += 2;
       n_mix = H * dv;
+    } else if (lc.mixer == DIS_MIX_SSM) {
+      const int H = lc.heads, P = lc.vdim, Ns = lc.ssm_state, G = lc.ssm_groups, C = L.conv_ch, inner = H * P;
+      const long long ld_b = (long long)C + inner;  // x | B | C | dt x
+      const float *vec = reinterpret_cast<const float *>(L.ssm_vec.ptr);
+      RET_CUDA(launch_stack_ssm_conv(M.proj, N, L.x_off, L.dt_off, C, H, P, lc.conv_taps, reinterpret_cast<const float *>(L.conv_w.ptr),
+                                     reinterpret_cast<const float *>(L.conv_b.ptr), vec, Rn.conv_state, sp, M.ssm, ld_b, M.dec, stream));
+      kl += lc.conv_taps > 1 ? 2 : 1;
+      const bool segments = M.light_seg && M.light_seg_a && max_span > stack_lightning_seg_tokens() && Ns <= 128 && P <= 128;
+      RET_CUDA(launch_stack_ssd(M.ssm, ld_b, inner + G * Ns, inner, C, H / G, M.dec, Rn.state, sp, M.mix, H, Ns, P, segments ? M.light_seg : nullptr,
+                                segments ? M.light_seg_a : nullptr, max_span, stream));
+      kl += segments ? 3 : 1;
+      RET_CUDA(launch_stack_ssm_out(M.mix, M.ssm, ld_b, M.proj, N, vec + 2 * H, reinterpret_cast<const float *>(L.norm_w.ptr), lc.ssm_norm_groups,
+                                    M.act, f32, T, H, P, eps, stream));
+      kl++;
+      n_mix = inner;
     } else if (lc.mixer == DIS_MIX_MINGRU) {
       int max_len = 0;
       for (auto &sh : stack_spans_h) max_len = std::max(max_len, sh.len);
@@ -1183,7 +1287,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     } else if (is_attn) {
       const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
       const bool par = lc.mixer == DIS_MIX_PARALLEL;
-      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, eps, lc.mask_chunk};
+      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, eps, lc.mask_chunk, lc.mask_window, lc.score_softcap};
       const float *qkn = reinterpret_cast<const float *>(L.qk_norm.ptr), *tpb = reinterpret_cast<const float *>(L.temp_pb.ptr);
       // the gains of the key norm follow those of the query norm: [H*d] then [G*d] (whole projection), or [d] then [d] (per head)
       const float *kn = qkn ? qkn + ((lc.attn_flags & DIS_ATTN_QK_NORM_HEAD) ? (size_t)d : (size_t)H * d) : nullptr;
@@ -1299,13 +1403,16 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       n_mix = H * dv;
     }
     RET_CUDA(gemm(M.act, f32, n_mix, L.w_o, 0, o_bias, M.y, T, W, n_mix, cap_tokens, nullptr, later));
-    pend_y = M.y; pend_post = norm_w(L, 1); pend_post_b = norm_b(L, 1);
+    pend_y = M.y; pend_post = norm_w(L, 1); pend_post_b = norm_b(L, 1); pend_hc = reinterpret_cast<const float *>(L.hc[0].ptr);
     if (lc.mlp == DIS_MLP_NONE) continue;
+    next_hc = reinterpret_cast<const float *>(L.hc[1].ptr);
     RET_CUDA(sublayer_in(norm_w(L, 2), norm_b(L, 2), L.canon2, Rn.cstate2));
     if (lc.mlp == DIS_MLP_DENSE) {
       RET_CUDA(dense_ff(L.w_gu, L.b_gu, L.w_down, L.b_down, lc.ff, lc.mlp_act, lc.limit, M.y, later));
     } else {
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
+      const int gc = L.gu_rows * ff;  // columns of an expert's first product: gate | up, or up alone
+      const bool shared_gate = lc.shared_ff > 0 && !(lc.mlp_flags & DIS_MLP_SHARED_PLAIN);
       // the always-on unit beside the experts: its dense product first (it borrows the buffers the experts' rows use afterwards);
       // the logit of its per-token gate is one more row of the router matrix, and the combine kernel adds it in
       const bool shared = lc.shared_ff > 0;
@@ -1332,10 +1439,11 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       };
       const float *router = reinterpret_cast<const float *>(L.router.ptr);
       RET_CUDA(launch_stack_route(M.hc, f32, router, T, W, E, top, lc.route_kind, reinterpret_cast<const float *>(L.correction.ptr), lc.route_groups,
-                                  lc.route_keep, shared ? router + (size_t)E * W : nullptr, M.r_sg, M.r_idx, M.r_wt, stream));
+                                  lc.route_keep, shared_gate ? router + (size_t)E * W : nullptr, M.r_sg, M.r_idx, M.r_wt, stream));
       RET_CUDA(launch_stack_moe_plan(M.r_idx, T, top, E, kStackGemmTile, M.counts, M.perm_tok, M.where, M.tiles, M.max_tiles, stream));
       // Large passes in bf16: one tensor-core product per expert over its rows.  The row counts come back to the host (one
       // small copy and a wait), so this path is not taken while a decode pass is being captured into a graph.
+      const float *sh_gate = shared_gate ? M.r_sg : nullptr;  // null: the shared unit joins the sum as it is
       if (M.moe_x && !stack_capturing && rows >= 64 * E && W % 8 == 0 && ff % 8 == 0) {
         RET_CUDA(launch_stack_moe_gather(M.hc, M.perm_tok, M.moe_x, rows, W, stream));
         RET_CUDA(cudaMemcpyAsync(M.h_counts, M.counts, (size_t)E * sizeof(int), cudaMemcpyDeviceToHost, stream));
@@ -1357,10 +1465,10 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
           cudaStream_t es = lane(e);
           TmaMap xm, am;
           RET_CUDA(make_tma_map_2d(&xm, reinterpret_cast<uint16_t *>(M.moe_x) + (size_t)off * W, (uint64_t)cnt, (uint64_t)W, (uint32_t)gemm_token_tile(cnt)));
-          const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(L.w_gu.ptr) + (size_t)e * 2 * ff * W, (uint64_t)2 * ff, (uint64_t)W, 128);
+          const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(L.w_gu.ptr) + (size_t)e * gc * W, (uint64_t)gc, (uint64_t)W, 128);
           if (!wm) return cudaErrorInvalidValue;
-          RET_CUDA(launch_gemm_partial(*wm, xm, M.proj + (size_t)off * 2 * ff, cnt, 2 * ff, W, 0, 1, es));
-          RET_CUDA(launch_stack_glu(M.proj + (size_t)off * 2 * ff, 1, 0, nullptr, reinterpret_cast<uint16_t *>(M.act) + (size_t)off * ff, f32, nullptr, cnt, ff,
+          RET_CUDA(launch_gemm_partial(*wm, xm, M.proj + (size_t)off * gc, cnt, gc, W, 0, 1, es));
+          RET_CUDA(launch_stack_glu(M.proj + (size_t)off * gc, 1, 0, nullptr, reinterpret_cast<uint16_t *>(M.act) + (size_t)off * ff, f32, nullptr, cnt, ff,
                                     lc.limit, lc.mlp_act, es));
           RET_CUDA(make_tma_map_2d(&am, reinterpret_cast<uint16_t *>(M.act) + (size_t)off * ff, (uint64_t)cnt, (uint64_t)ff, (uint32_t)gemm_token_tile(cnt)));
           const TmaMap *dm = stack_map(reinterpret_cast<const uint16_t *>(L.w_down.ptr) + (size_t)e * W * ff, (uint64_t)W, (uint64_t)ff, 128);
@@ -1375,15 +1483,15 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
             RET_CUDA(cudaStreamWaitEvent(stream, M.ev_join[k], 0));
           }
         RET_CUDA(join_shared());
-        RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? sh_src : nullptr, sh_parts, sh_stride, M.r_sg, M.y, T, W, top, stream));
-        pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
+        RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? sh_src : nullptr, sh_parts, sh_stride, sh_gate, M.y, T, W, top, stream));
+        pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3); pend_hc = reinterpret_cast<const float *>(L.hc[1].ptr);
         continue;
       }
       const int tiles_cap = std::min(M.max_tiles, (rows + kStackGemmTile - 1) / kStackGemmTile + E);
       StackGemm g;
       g.A = M.hc; g.a_f32 = f32; g.lda = W; g.a_gather = M.perm_tok;
-      g.W = L.w_gu.ptr; g.w_f32 = L.w_gu.f32; g.ldw = W; g.w_bs = (long long)2 * ff * W;
-      g.out = M.proj; g.ldo = 2 * ff; g.M = rows; g.N = 2 * ff; g.K = W;
+      g.W = L.w_gu.ptr; g.w_f32 = L.w_gu.f32; g.ldw = W; g.w_bs = (long long)gc * W;
+      g.out = M.proj; g.ldo = gc; g.M = rows; g.N = gc; g.K = W;
       g.tiles = M.tiles; g.max_tiles = tiles_cap;
       RET_CUDA(launch_stack_gemm(g, stream));
       StackGemm dn;
@@ -1392,24 +1500,25 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       dn.out = M.rows_out; dn.ldo = W; dn.M = rows; dn.N = W; dn.K = ff;
       dn.tiles = M.tiles; dn.max_tiles = tiles_cap;
       static const bool few_glu = getenv("DIS_STACK_FEW_GLU") && atoi(getenv("DIS_STACK_FEW_GLU")) != 0;  // opt-in: measured slower (0.547 against 0.534 ms per step)
-      if (few_glu && stack_gemm_few_rows(dn)) {  // a handful of rows: the down product's loader applies the gated unit to the gate | up rows
+      if (few_glu && L.gu_rows == 2 && stack_gemm_few_rows(dn)) {  // a handful of rows: the down product's loader applies the gated unit to the gate | up rows
         dn.A = M.proj; dn.a_f32 = true; dn.lda = 2 * ff; dn.a_glu = lc.mlp_act + 1; dn.a_limit = lc.limit;
         kl--;
       } else RET_CUDA(launch_stack_glu(M.proj, 1, 0, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
       RET_CUDA(launch_stack_gemm(dn, stream));
       RET_CUDA(join_shared());
-      RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? sh_src : nullptr, sh_parts, sh_stride, M.r_sg, M.y, T, W, top, stream));
+      RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, shared ? sh_src : nullptr, sh_parts, sh_stride, sh_gate, M.y, T, W, top, stream));
       kl += 6;
     }
-    pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
+    pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3); pend_hc = reinterpret_cast<const float *>(L.hc[1].ptr);
   }
+  next_hc = nullptr;
   // the last sublayer's output joins the residual; rows that need logits get the final norm and the head
   if (single || ln) RET_CUDA(sublayer_in(nullptr, nullptr, nullptr, nullptr));
   else { RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++; }
   if (R <= 0) return cudaSuccess;
   if (ln) RET_CUDA(launch_stack_final_ln(M.x, mt.d<int>(mt.o_rowmap), reinterpret_cast<const float *>(M.final_w.ptr),
                                          rms ? nullptr : reinterpret_cast<const float *>(M.final_b.ptr), M.xr, f32, R, W, eps, M.c.logit_scale,
-                                         stream));
+                                         n_streams, stream));
   else RET_CUDA(launch_stack_final_norm(M.x, mt.d<int>(mt.o_rowmap), M.final_g, M.xr, f32, R, W, eps, stream));
   kl++;
   RET_CUDA(gemm(M.xr, f32, W, M.head, 0, nullptr, M.logits, R, M.c.vocab, W, M.max_rows));

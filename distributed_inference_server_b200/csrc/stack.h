@@ -48,9 +48,16 @@ struct StackSpans {  // device arrays of the pass
   int T, n_spans;
 };
 
-// x = embed[token] * scale; x0 (when given) receives the same rows
-cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, float *x, float *x0, float scale, int T, int W,
-                               cudaStream_t st);
+// x = embed[token] * scale (+ a sinusoidal position vector when pos_freq, a table of W/2 frequencies, is given), written to each
+// of the token's `streams` residual streams ([T][streams][W]); x0 (when given) receives the same rows once
+cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, const int *pos, const double *pos_freq, float *x,
+                               float *x0, float scale, int T, int W, int streams, cudaStream_t st);
+// Pre-norm boundary over `streams` residual streams xs [T][streams][W]: the product before (y, as slices + bias) joins every
+// stream through the coefficients `prev` of its sublayer (in | out | mix; null: x += y), then the coming sublayer's input
+// u = sum_s next[s] x_s (null: x_0) is RMS-normed with the gain vector pre_w into hc (pre_w null: only the streams move on).
+cudaError_t launch_stack_boundary_hc(float *xs, int streams, const float *y, int n_part, long long stride, const float *bias,
+                                     const float *prev, const float *next, const float *pre_w, void *hc, bool f32, int T, int W, float eps,
+                                     cudaStream_t st);
 // x += unit_rms(y) * post (when y), then hn = unit_rms(x) * pre (when hn).  post / pre: device scalars.
 cudaError_t launch_stack_resid_norm(float *x, const float *y, const float *post, const float *pre, float *hn, int T, int W,
                                     float eps, cudaStream_t st);
@@ -71,8 +78,9 @@ cudaError_t launch_stack_boundary_ln(float *x, const float *y, int n_part, long 
 // rms: both norms are v / sqrt(mean(v^2) + eps) * w (gain vectors, no mean taken off, no bias vectors)
 // out = LN(x[row_map[r]]) * scale: a factor on the logits is applied to the head's input (head (s v) = s (head v)).
 // b == null: the RMS form with the gain vector w
+// streams > 1: the row is the sum of the token's residual streams (x is [T][streams][W])
 cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const float *w, const float *b, void *out, bool f32, int R, int W,
-                                  float eps, float scale, cudaStream_t st);
+                                  float eps, float scale, int streams, cudaStream_t st);
 cudaError_t launch_stack_scale(float *v, long long n, float s, cudaStream_t st);
 // v = cap * tanh(v / cap)
 cudaError_t launch_stack_softcap(float *v, long long n, float cap, cudaStream_t st);
@@ -94,6 +102,23 @@ size_t stack_lightning_seg_decay_floats(int cap_tokens, int max_spans, int H, in
 cudaError_t launch_stack_gla(const float *proj, long long ld, int q_off, int k_off, int v_off, const float *dec, float *state,
                              const StackSpans &sp, float *o, int H, int d, int dv, float *seg, float *seg_a, int max_len,
                              cudaStream_t st);
+// State-space mixer (DIS_MIX_SSM), three steps around the recurrence kernel of gated linear attention.
+// 1. proj [T][ld] holds z | x | B | C | dt as projected.  The C = inner + 2 G N channels from x_off on pass a causal depthwise
+//    convolution over time (cw [C][taps], last tap = the current token; the taps - 1 inputs before a span come from cstate
+//    [slots][taps-1][C], zeros before position 0) plus cb, then SiLU -> buf [T][ld_b] columns 0 .. C (x | B | C).  dt = softplus(
+//    proj[dt_off + h] + vec[h]) (vec = dt_bias | A_log | D, [3H]); buf columns C .. C + inner receive dt * x (the recurrence's
+//    values) and dec [T][H] the decays exp(-exp(A_log[h]) dt).  A second launch moves cstate on to the span's last inputs.
+cudaError_t launch_stack_ssm_conv(const float *proj, long long ld, int x_off, int dt_off, int C, int H, int P, int taps, const float *cw,
+                                  const float *cb, const float *vec, float *cstate, const StackSpans &sp, float *buf, long long ld_b,
+                                  float *dec, cudaStream_t st);
+// 2. S [N][P] per head: S = dec[t][h] S + B_t (dt x_t)^T, o_t = S^T C_t.  buf as above (B at b_off, C at c_off, dt x at v_off;
+//    head h reads the B, C of group h / hpg); state [slots][H][N][P]; o [T][H*P]; seg / seg_a as for gated linear attention.
+cudaError_t launch_stack_ssd(const float *buf, long long ld_b, int c_off, int b_off, int v_off, int hpg, const float *dec, float *state,
+                             const StackSpans &sp, float *o, int H, int N, int P, float *seg, float *seg_a, int max_len, cudaStream_t st);
+// 3. y = (o + D[h] x) silu(z), RMS-normed in `parts` equal parts of H*P (each by its own mean square), times w -> out [T][H*P] in
+//    the compute type.  x: buf column 0 on (row stride ld_b), z: proj column 0 on (row stride ld).
+cudaError_t launch_stack_ssm_out(const float *o, const float *buf, long long ld_b, const float *z, long long ld, const float *D,
+                                 const float *w, int parts, void *out, bool f32, int T, int H, int P, float eps, cudaStream_t st);
 // out[t][off + h*dv + j] = scale * unit_rms_over_head(o[t][h])[j] * w[j] * silu(gate[t][h*dv + j]); out [T][ldo] compute type
 cudaError_t launch_stack_headnorm_silu(const float *o, const float *w, const float *gate, long long ldg, void *out, long long ldo,
                                        int off, float scale, bool f32, int T, int H, int dv, float eps, cudaStream_t st);
@@ -103,7 +128,16 @@ struct StackAttn {
   unsigned flags;  // DIS_ATTN_*
   float scale, eps;
   int chunk;       // > 0: position i sees only keys from floor(i / chunk) * chunk on
+  int window = 0;  // > 0: position i sees only the keys j with i - j < window
+  float softcap = 0.f;  // > 0: score <- softcap * tanh(score / softcap), after the factor `scale` (softmax weights only)
 };
+// first key position the query at position `pos` may see (both masks are monotone in pos, so a block of consecutive queries
+// starts its walk at the bound of its first token)
+__host__ __device__ inline int stack_attn_row_lo(const StackAttn &c, int pos) {
+  int lo = c.chunk > 0 ? pos / c.chunk * c.chunk : 0;
+  if (c.window > 0 && pos - c.window + 1 > lo) lo = pos - c.window + 1;
+  return lo;
+}
 // Per token: (bias, one entry per column of proj), query/key norm over the whole projection (gains qn [H*d], kn [G*d]) or per
 // head (DIS_ATTN_QK_NORM_HEAD: gains [d] shared by the heads), rotation of the first rot_dims coordinates of every head by
 // pos * freq[i] (pairs i, i + rot_dims/2); queries to qf [T][H*d]; rotated keys and the values (own projection at v_off, or the
@@ -242,6 +276,12 @@ struct StackLayer {
   StackTensor router;                      // [E][W] fp32; with a shared expert one more row: the logit of its per-token gate
   StackTensor correction;                  // [E] fp32: added to the sigmoid scores when the experts are chosen
   StackTensor w_sgu, w_sdown;              // shared expert: [2 shared_ff][W], [W][shared_ff]
+  // an ungated activation (DIS_ACT_RELU2) has no gate rows: w_gu / w_sgu hold [ff][W] per unit, named "up"
+  int gu_rows = 2;                         // rows of w_gu per hidden unit: 2 (gate | up) or 1
+  StackTensor hc[2];                       // residual streams: coefficients of the mixer's and the feed-forward's frame, in[S] | out[S] | mix[S][S] fp32
+  // state-space mixer: w_in rows z | x | B | C | dt; norm_w = gain of the group norm [H*vdim]
+  StackTensor conv_w, conv_b, ssm_vec;     // [C][taps], [C], dt_bias | A_log | D [3H], all fp32
+  int x_off = 0, dt_off = 0, conv_ch = 0;
 };
 
 // One execution of a layer inside a forward pass.  Without a loop every layer runs once; a looped stretch contributes one
@@ -254,6 +294,7 @@ struct StackRun {
   void *kpool = nullptr, *vpool = nullptr;  // attention: [pages*page_size][G*dim], [..][G*vdim]
   float *state = nullptr;   // lightning / gated linear attention [slots][H][d][dv]; mingru [slots][n]
   float *cstate1 = nullptr, *cstate2 = nullptr;      // [slots][taps-1][W]
+  float *conv_state = nullptr;                       // state-space mixer: the convolution's last inputs [slots][conv_taps-1][C]
 };
 
 struct StackModel {
@@ -265,6 +306,9 @@ struct StackModel {
   float *final_g = nullptr;
   StackTensor final_w, final_b;    // layer-norm form of the final norm
   StackTensor loop_in, loop_step;  // [W][2W] compute type, [times][W] fp32
+  double *pos_freq = nullptr;      // sinusoidal positions: base^(-2i/W), i < (W + 1) / 2
+  float *ssm = nullptr;            // state-space mixer: x | B | C after convolution and SiLU, then dt x, per token
+  size_t ssm_ld = 0;
   float *x0 = nullptr;             // the scaled embedding rows of the pass (input of every loop pass)
   void *xcat = nullptr;            // [x ; x0] in the compute type
   float *dec = nullptr;            // gated linear attention: the decays of the pass [T][H*d]

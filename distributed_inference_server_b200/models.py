@@ -23,6 +23,13 @@ engine's description of the model and names every tensor.  Two families exist:
             keys and values instead of projecting its own; the feed-forward is a mixture of SiLU-gated experts chosen by a
             sigmoid router with a correction vector and a limit on the groups of experts a token may use, plus a shared
             expert behind a sigmoid gate; the logits pass through a tanh soft cap.
+  Goperax   a layer-list decoder of the same engine in the pre-norm frame (RMS norms with gain vectors in front of the
+            sublayers only) whose residual is several streams mixed by small learned matrices around every sublayer; scaled
+            embedding plus a sinusoidal position vector, logits from the embedding table itself; a stretch of layers that runs
+            several times in a row with nothing in between; mixers `attention` (grouped-query, values = keys, no rotation, a
+            tanh soft cap on the scores, a sliding window, and a softmax whose denominator carries one extra 1) and `mamba2`
+            (selective state space with a short causal convolution, gated and group-normalised); feed-forward of ungated
+            squared-ReLU units, dense or as a mixture chosen by a softmax router, with an optional always-on shared unit.
 
 The reference has no model loading at all (crates/inference/src/worker.rs:1 is empty).
 """
@@ -40,7 +47,9 @@ import numpy as np
 from . import binding as B
 
 _MIXERS = {"lightning": B.MIX_LIGHTNING, "mingru": B.MIX_MINGRU, "latent_attention": B.MIX_LATENT,
-           "attention": B.MIX_ATTENTION, "parallel": B.MIX_PARALLEL}
+           "attention": B.MIX_ATTENTION, "parallel": B.MIX_PARALLEL, "ssm": B.MIX_SSM}
+_ACTS = {"clamped": B.ACT_CLAMPED, "gelu_tanh": B.ACT_GELU_TANH, "silu": B.ACT_SILU, "relu2": B.ACT_RELU2}
+_ROUTES = {"softmax_top": B.ROUTE_SOFTMAX_TOP, "sigmoid_groups": B.ROUTE_SIGMOID_GROUPS, "softmax_all": B.ROUTE_SOFTMAX_ALL}
 
 
 @dataclass
@@ -76,12 +85,23 @@ class LayerSpec:
     gla_tau: float = 1.0
     mix_scale: float = 1.0
     gla_scale: float = 1.0
-    mlp_act: str = "clamped"  # clamped (with biases) | gelu_tanh (without) | silu (without)
+    mlp_act: str = "clamped"  # clamped (with biases) | gelu_tanh (without) | silu (without) | relu2 (ungated, without)
     mask_chunk: int = 0  # attention: chunked causal mask (0 = plain causal)
-    route: str = "softmax_top"  # softmax_top | sigmoid_groups
+    route: str = "softmax_top"  # softmax_top | sigmoid_groups | softmax_all
     route_groups: int = 0
     route_keep: int = 0
     shared_ff: int = 0  # mixture of experts: hidden size of the shared expert (0 = none)
+    mask_window: int = 0  # attention: sliding window (0 = none)
+    score_softcap: float = 0.0  # attention: tanh soft cap on the scaled scores (0 = none)
+    ssm_state: int = 0  # state-space mixer: state size per head, groups sharing B and C, convolution taps, norm parts
+    ssm_groups: int = 0
+    conv_taps: int = 0
+    ssm_norm_groups: int = 1
+    shared_plain: bool = False  # the shared expert joins the sum without a gate
+
+    @property
+    def gated(self) -> bool:
+        return self.mlp_act != "relu2"
 
 
 @dataclass
@@ -98,6 +118,12 @@ class StackSpec:
     logit_scale: float = 1.0
     loop: Tuple[int, int, int] = (0, 0, 0)  # start, stop, times (times 0 = no loop)
     logit_softcap: float = 0.0  # c > 0: logits -> c tanh(logits / c)
+    pre_norm: bool = False  # sublayers are x += f(norm(x)): no norms behind them
+    streams: int = 0  # residual streams mixed around every sublayer (0 = one plain residual); needs pre_norm
+    pos_sinus: bool = False  # a sinusoidal position vector joins the scaled embedding
+    pos_base: float = 10000.0
+    loop_plain: bool = False  # the loop's passes follow each other without an input projection
+    tied_head: bool = False  # logits from the embedding table: the file has no "head"
 
     def layer_runs(self) -> List[int]:
         """Layer index of every layer run of one forward pass, the looped stretch repeated."""
@@ -109,20 +135,26 @@ class StackSpec:
     def tensor_shapes(self) -> Dict[str, Tuple[int, ...]]:
         """Every tensor of the model file, by name."""
         W, out = self.width, {"embed": (self.vocab, self.width), "head": (self.vocab, self.width)}
+        if self.tied_head:
+            del out["head"]
         vec = self.norm_kind in ("layer", "rms")
+        post = not self.pre_norm
 
         def norm(name):
             out[name] = (W,) if vec else ()
             if self.norm_kind == "layer":
                 out[name + ".b"] = (W,)
         norm("final.norm")
-        if self.loop[2] > 0:
+        if self.loop[2] > 0 and not self.loop_plain:
             out["loop.in"] = (W, 2 * W)
             out["loop.step"] = (self.loop[2], W)
         for i, L in enumerate(self.layers):
             p = f"l{i}."
             norm(p + "norm1")
-            norm(p + "norm1b")
+            if post:
+                norm(p + "norm1b")
+            for q in ((1,) if L.mlp == "none" else (1, 2)) if self.streams > 0 else ():
+                out.update({f"{p}hc{q}.in": (self.streams,), f"{p}hc{q}.out": (self.streams,), f"{p}hc{q}.mix": (self.streams, self.streams)})
             if self.canon_taps >= 1:
                 out[p + "canon1"] = (W, self.canon_taps)
             if L.mixer == "lightning":
@@ -131,6 +163,11 @@ class StackSpec:
             elif L.mixer == "mingru":
                 out.update({p + "mix.z": (L.width, W), p + "mix.z.b": (L.width,), p + "mix.x": (L.width, W), p + "mix.x.b": (L.width,),
                             p + "mix.g": (L.width, W), p + "mix.o": (W, L.width)})
+            elif L.mixer == "ssm":
+                inner, gn = L.heads * L.vdim, L.ssm_groups * L.ssm_state
+                out.update({p + "mix.in": (2 * inner + 2 * gn + L.heads, W), p + "mix.conv": (inner + 2 * gn, L.conv_taps),
+                            p + "mix.conv.b": (inner + 2 * gn,), p + "mix.dt_bias": (L.heads,), p + "mix.A_log": (L.heads,),
+                            p + "mix.D": (L.heads,), p + "mix.norm": (inner,), p + "mix.o": (W, inner)})
             elif L.mixer in ("attention", "parallel"):
                 a = p + ("mix.left." if L.mixer == "parallel" else "mix.")
                 own = L.kv_from < 0  # a layer that reads another layer's cache has nothing of the keys and values
@@ -171,10 +208,22 @@ class StackSpec:
             if L.mlp == "none":
                 continue
             norm(p + "norm2")
-            norm(p + "norm2b")
+            if post:
+                norm(p + "norm2b")
             if self.canon_taps >= 1:
                 out[p + "canon2"] = (W, self.canon_taps)
-            if L.mlp == "dense" and L.mlp_act in ("gelu_tanh", "silu"):
+            if not L.gated:  # ungated units: "up" and "down" only
+                if L.mlp == "dense":
+                    out.update({p + "mlp.up": (L.ff, W), p + "mlp.down": (W, L.ff)})
+                else:
+                    out[p + "mlp.router"] = (L.experts, W)
+                    for e in range(L.experts):
+                        out.update({f"{p}mlp.e{e}.up": (L.ff, W), f"{p}mlp.e{e}.down": (W, L.ff)})
+                    if L.shared_ff > 0:
+                        out.update({p + "mlp.shared.up": (L.shared_ff, W), p + "mlp.shared.down": (W, L.shared_ff)})
+                        if not L.shared_plain:
+                            out[p + "mlp.shared.sg"] = (1, W)
+            elif L.mlp == "dense" and L.mlp_act in ("gelu_tanh", "silu"):
                 out.update({p + "mlp.gate": (L.ff, W), p + "mlp.up": (L.ff, W), p + "mlp.down": (W, L.ff)})
             elif L.mlp == "dense":
                 out.update({p + "mlp.gate": (L.ff, W), p + "mlp.gate.b": (L.ff,), p + "mlp.up": (L.ff, W), p + "mlp.up.b": (L.ff,),
@@ -187,7 +236,9 @@ class StackSpec:
                     out[p + "mlp.correction"] = (L.experts,)
                 if L.shared_ff > 0:
                     out.update({p + "mlp.shared.gate": (L.shared_ff, W), p + "mlp.shared.up": (L.shared_ff, W),
-                                p + "mlp.shared.down": (W, L.shared_ff), p + "mlp.shared.sg": (1, W)})
+                                p + "mlp.shared.down": (W, L.shared_ff)})
+                    if not L.shared_plain:
+                        out[p + "mlp.shared.sg"] = (1, W)
         return out
 
     def c(self, max_ctx: int, max_logit_rows: int, f32: bool):
@@ -210,14 +261,20 @@ class StackSpec:
             c.rot_factor, c.rot_low, c.rot_high, c.rot_original = L.rot_factor, L.rot_low, L.rot_high, L.rot_original
             c.gla_heads, c.gla_dim, c.gla_vdim, c.gla_rank = L.gla_heads, L.gla_dim, L.gla_vdim, L.gla_rank
             c.gla_tau, c.mix_scale, c.gla_scale = L.gla_tau, L.mix_scale, L.gla_scale
-            c.mlp_act = {"clamped": B.ACT_CLAMPED, "gelu_tanh": B.ACT_GELU_TANH, "silu": B.ACT_SILU}[L.mlp_act]
+            c.mlp_act = _ACTS[L.mlp_act]
             c.mask_chunk, c.shared_ff = L.mask_chunk, L.shared_ff
-            c.route_kind = {"softmax_top": B.ROUTE_SOFTMAX_TOP, "sigmoid_groups": B.ROUTE_SIGMOID_GROUPS}[L.route]
+            c.route_kind = _ROUTES[L.route]
             c.route_groups, c.route_keep = L.route_groups, L.route_keep
+            c.mask_window, c.score_softcap = L.mask_window, L.score_softcap
+            c.ssm_state, c.ssm_groups, c.conv_taps, c.ssm_norm_groups = L.ssm_state, L.ssm_groups, L.conv_taps, L.ssm_norm_groups
+            c.mlp_flags = B.MLP_SHARED_PLAIN if L.shared_plain else 0
         sc = B.StackConfig(self.vocab, self.width, len(self.layers), self.canon_taps, max_ctx, max_logit_rows,
                            B.F32 if f32 else B.BF16, self.norm_eps, arr,
                            {"rms_scalar": B.NORM_RMS_SCALAR, "layer": B.NORM_LAYER, "rms": B.NORM_RMS}[self.norm_kind],
-                           self.embed_scale, self.logit_scale, *self.loop, self.logit_softcap)
+                           self.embed_scale, self.logit_scale, *self.loop, self.logit_softcap,
+                           (B.FRAME_PRE_NORM if self.pre_norm else 0) | (B.FRAME_POS_SINUS if self.pos_sinus else 0) |
+                           (B.FRAME_LOOP_PLAIN if self.loop_plain else 0) | (B.FRAME_TIED_HEAD if self.tied_head else 0),
+                           self.streams, self.pos_base)
         return sc, keep
 
 
@@ -358,6 +415,58 @@ def fakonex_spec(cfg: dict) -> StackSpec:
                      "rms", logit_softcap=float(cfg.get("logit_softcap") or 0.0))
 
 
+def goperax_spec(cfg: dict) -> StackSpec:
+    """Goperax's config.json -> StackSpec: every size and every constant that may differ between models comes from the file;
+    what the design fixes (the base of the position vector, the activation, the unit sink) is set here.  A part the file
+    leaves out is off: no `mask` = the whole past, no `softcap` = none, no `shared` = no shared unit, no `loop` = every layer
+    once, no `streams` = one plain residual."""
+    layers = []
+    for i, ly in enumerate(cfg["layers"]):
+        kind, mx = ly["type"], ly["mixer"]
+        if kind == "attention":
+            L = LayerSpec("attention")
+            L.heads, L.kv_heads, L.dim, L.vdim = int(mx["heads"]), int(mx["kv_heads"]), int(mx["dim"]), int(mx["vdim"])
+            if L.heads % L.kv_heads:
+                raise ValueError(f"layer {i}: heads must be a multiple of kv_heads")
+            if L.vdim != L.dim:
+                raise ValueError(f"layer {i}: the values are the keys, so vdim must equal dim")
+            L.scale = float(mx["scale"])
+            L.attn_flags = B.ATTN_V_IS_K | B.ATTN_SINK_UNIT
+            L.mask_window = int((mx.get("mask") or {}).get("size", 0))
+            L.score_softcap = float(mx.get("softcap") or 0.0)
+        elif kind == "mamba2":
+            L = LayerSpec("ssm")
+            L.heads, L.vdim, L.ssm_state, L.ssm_groups = int(mx["heads"]), int(mx["vdim"]), int(mx["state"]), int(mx["groups"])
+            L.conv_taps, L.ssm_norm_groups = int(mx["conv"]), int(mx.get("norm_groups", 1))
+            if L.ssm_groups < 1 or L.heads % L.ssm_groups:
+                raise ValueError(f"layer {i}: heads must be a multiple of groups")
+            if L.ssm_norm_groups < 1 or (L.heads * L.vdim) % L.ssm_norm_groups:
+                raise ValueError(f"layer {i}: norm_groups must divide heads * vdim")
+        else:
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        ml = ly.get("mlp")
+        if ml is not None:
+            L.mlp_act = "relu2"
+            if ml.get("kind") == "dense":
+                L.mlp, L.ff = "dense", int(ml["ff"])
+            elif ml.get("kind") == "moe":
+                L.mlp, L.ff, L.route = "moe", int(ml["expert"]["ff"]), "softmax_all"
+                L.experts, L.top = int(ml["router"]["experts"]), int(ml["router"]["top"])
+                sh = ml.get("shared")
+                if sh:
+                    L.shared_ff, L.shared_plain = int(sh["ff"]), True
+            else:
+                raise ValueError(f"layer {i}: unknown feed-forward kind {ml.get('kind')!r}")
+        layers.append(L)
+    lp = cfg.get("loop")
+    loop = (int(lp["start"]), int(lp["stop"]), int(lp["times"])) if lp and int(lp.get("times", 0)) > 0 else (0, 0, 0)
+    if loop[2] > 0 and not 0 <= loop[0] < loop[1] <= len(layers):
+        raise ValueError("loop: start < stop must lie inside the layer list")
+    return StackSpec("Goperax", int(cfg["vocab"]), int(cfg["width"]), layers, 0, float((cfg.get("norm") or {}).get("eps", 1e-5)), "rms",
+                     embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)), loop=loop, pre_norm=True,
+                     streams=int(cfg.get("streams") or 0), pos_sinus=True, pos_base=10000.0, loop_plain=True, tied_head=True)
+
+
 def llama_shape(cfg: dict):
     """A Hugging Face style Llama config.json -> ModelShape."""
     from .worker import ModelShape
@@ -373,6 +482,7 @@ ARCHITECTURES: Dict[str, Tuple[str, Callable[..., object]]] = {
     "Kidolorn": ("stack", kidolorn_spec),
     "Motolix": ("stack", motolix_spec),
     "Fakonex": ("stack", fakonex_spec),
+    "Goperax": ("stack", goperax_spec),
     "LlamaForCausalLM": ("llama", llama_shape),
     "llama": ("llama", llama_shape),
 }
@@ -514,6 +624,18 @@ def random_tensors(spec: StackSpec, seed: int = 0, scale: float = 1.0) -> Dict[s
             a = rng.normal(0, 1.0, shape).astype(np.float32)
         elif leaf == "correction":
             a = rng.normal(0, 0.3, shape).astype(np.float32)
+        elif ".hc" in name:  # stream coefficients: readers and writers near 1 / S and 1, mixers near the identity
+            n = shape[0]
+            a = {"in": rng.normal(1.0 / n, 0.1, shape), "out": rng.normal(1.0, 0.2, shape),
+                 "mix": np.eye(n) + rng.normal(0, 0.1, shape)}[leaf].astype(np.float32)
+        elif leaf == "dt_bias":
+            a = rng.normal(-1.0, 1.0, shape).astype(np.float32)
+        elif leaf == "A_log":
+            a = rng.uniform(-2.0, 1.0, shape).astype(np.float32)
+        elif leaf == "D":
+            a = rng.normal(1.0, 0.3, shape).astype(np.float32)
+        elif leaf == "conv":
+            a = rng.normal(0, 0.5, shape).astype(np.float32)
         elif leaf == "b":
             a = rng.normal(0, 0.3, shape).astype(np.float32)
         elif name in ("embed",):

@@ -31,7 +31,9 @@ extern "C" {
 #endif
 
 #define DIS_API __attribute__((visibility("default")))
-#define DIS_ABI_VERSION 4 /* 2: 16-byte request ids, logprob on token events / callback, dis_serving_cancel; 3: dis_layer_config and dis_stack_config grew (attention and parallel mixers, layer norms, layer loops); 4: they grew again (chunked mask, sink, per-head query/key norm and output gate of attention, shared key/value cache, grouped sigmoid router, shared expert, RMS norms with gain vectors, logit soft cap) */
+#define DIS_ABI_VERSION 5 /* 2: 16-byte request ids, logprob on token events / callback, dis_serving_cancel; 3: dis_layer_config and dis_stack_config grew (attention and parallel mixers, layer norms, layer loops); 4: they grew again (chunked mask, sink, per-head query/key norm and output gate of attention, shared key/value cache, grouped sigmoid router, shared expert, RMS norms with gain vectors, logit soft cap); 5: and again (state-space mixer, sliding window, score soft cap and unit sink of
+                             attention, ungated squared-ReLU units, softmax-over-all router, ungated shared expert, residual streams, pre-norm frame,
+                             sinusoidal positions, loops without an input projection, head tied to the embedding) */
 
 /* ---- status codes: WorkerError, crates/core/src/error.rs:115-128 ------------------------------ */
 typedef enum dis_status {
@@ -426,13 +428,20 @@ typedef enum dis_mixer_kind {
                             with a per-head sink term in the denominator and a sigmoid output gate */
   DIS_MIX_ATTENTION = 3, /* grouped-query attention over paged keys and values; what it does beyond q k^T -> weights -> values
                             is chosen by attn_flags */
-  DIS_MIX_PARALLEL = 4   /* two mixers read the same input: DIS_MIX_ATTENTION (the fields above) and gated linear attention
+  DIS_MIX_PARALLEL = 4,  /* two mixers read the same input: DIS_MIX_ATTENTION (the fields above) and gated linear attention
                             (the gla_* fields); their outputs are added with the weights mix_scale / gla_scale */
+  DIS_MIX_SSM = 5        /* selective state-space mixer (state-space duality form): one projection "in" gives z | x | B | C | dt;
+                            x, B, C pass a causal depthwise convolution ("conv" [channels][conv_taps], last tap = current token, bias
+                            "conv.b") and SiLU; dt = softplus(dt + "dt_bias"); per head (heads, value size vdim, state size ssm_state; head
+                            h reads B, C of group h / (heads / ssm_groups)) S = exp(-exp("A_log"[h]) dt) S + dt B x^T, y = S^T C + "D"[h] x;
+                            y silu(z) is RMS-normed in ssm_norm_groups equal parts, times "norm", then projected by "o".  Sequence state:
+                            S (fp32) and the convolution's last conv_taps - 1 inputs */
 } dis_mixer_kind;
 typedef enum dis_mlp_kind { DIS_MLP_NONE = 0, DIS_MLP_DENSE = 1, DIS_MLP_MOE = 2 } dis_mlp_kind;
 /* Feed-forward unit.  CLAMPED: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, +-limit), biases on every
  * matrix.  GELU_TANH: gelu_tanh(g) u, no biases.  SILU: g sigmoid(g) u, no biases. */
-typedef enum dis_mlp_act { DIS_ACT_CLAMPED = 0, DIS_ACT_GELU_TANH = 1, DIS_ACT_SILU = 2 } dis_mlp_act;
+typedef enum dis_mlp_act { DIS_ACT_CLAMPED = 0, DIS_ACT_GELU_TANH = 1, DIS_ACT_SILU = 2, DIS_ACT_RELU2 = 3 } dis_mlp_act;
+/* RELU2 is an ungated unit: "down" (relu("up" h))^2 -- there is no "gate" matrix, in dense layers, experts and shared experts alike. */
 /* Norms around the sublayers.  RMS_SCALAR: x / rms(x) times one scalar gain (tensor of shape []).  LAYER: (x - mean) / sqrt(var +
  * eps) * w + b with vectors w ("<name>") and b ("<name>.b").  RMS: x / rms(x) * w with a gain vector w ("<name>"), no bias. */
 typedef enum dis_norm_kind { DIS_NORM_RMS_SCALAR = 0, DIS_NORM_LAYER = 1, DIS_NORM_RMS = 2 } dis_norm_kind;
@@ -442,7 +451,10 @@ typedef enum dis_norm_kind { DIS_NORM_RMS_SCALAR = 0, DIS_NORM_LAYER = 1, DIS_NO
  * contiguous blocks of experts / route_groups each; a block is ranked by c_max1 + c_max2, its top two entries of c; experts of
  * blocks ranked below route_keep drop out (c = -inf).  The `top` largest remaining c are chosen (ties: lowest index), and
  * expert e of the chosen set S gets the weight s_e / (sum_{S} s + 1e-20) -- the correction steers the choice only. */
-typedef enum dis_route_kind { DIS_ROUTE_SOFTMAX_TOP = 0, DIS_ROUTE_SIGMOID_GROUPS = 1 } dis_route_kind;
+/* SOFTMAX_ALL: s = softmax(z) over all experts, the `top` largest s (ties: lowest index), weights s_e / (sum_{S} s + 1e-20).  The
+ * common factor of the softmax cancels, so choice and weights are those of SOFTMAX_TOP; the kind exists so that a configuration can
+ * say what its file says. */
+typedef enum dis_route_kind { DIS_ROUTE_SOFTMAX_TOP = 0, DIS_ROUTE_SIGMOID_GROUPS = 1, DIS_ROUTE_SOFTMAX_ALL = 2 } dis_route_kind;
 /* dis_layer_config.attn_flags */
 #define DIS_ATTN_SIGMOID   1u   /* weight of a visible key = sigmoid(score * temp[h] + pb[h]) (per-head tensors "temp", "pb"),
                                    not normalised over the keys; without the flag: softmax over the visible keys */
@@ -459,6 +471,16 @@ typedef enum dis_route_kind { DIS_ROUTE_SOFTMAX_TOP = 0, DIS_ROUTE_SIGMOID_GROUP
                                    "sink"; the extra term adds nothing to the numerator and the score scale does not apply to it */
 #define DIS_ATTN_GATE    256u   /* out_h <- out_h * sigmoid(("g" u)[h]) in front of the output projection, u being the mixer's input
                                    and "g" a [heads][width] matrix: a scalar gate per (token, head) */
+#define DIS_ATTN_SINK_UNIT 512u /* softmax only: one more term of logit 0 in the denominator, exp(score_j) / (1 + sum_j exp(score_j)); no
+                                   tensor */
+/* dis_layer_config.mlp_flags */
+#define DIS_MLP_SHARED_PLAIN 1u /* the shared expert's output joins the experts' sum as it is: there is no "shared.sg" gate */
+/* dis_stack_config.frame_flags */
+#define DIS_FRAME_PRE_NORM   1u /* a sublayer is x += f(norm(x)): no norm behind the sublayer (no "norm1b" / "norm2b") */
+#define DIS_FRAME_POS_SINUS  2u /* the embedding row (after embed_scale) gets a sinusoidal position vector added: entry 2i =
+                                   sin(p pos_base^(-2i/width)), entry 2i+1 = cos of the same angle, p the position in the sequence */
+#define DIS_FRAME_LOOP_PLAIN 4u /* passes of the loop follow each other directly: no "loop.in" / "loop.step" */
+#define DIS_FRAME_TIED_HEAD  8u /* the logits are products with the embedding table itself (without embed_scale): no "head" tensor */
 
 typedef struct dis_layer_config {
   int32_t mixer;                 /* dis_mixer_kind */
@@ -495,6 +517,12 @@ typedef struct dis_layer_config {
   int32_t shared_ff;             /* mixture of experts: hidden size of an always-on unit ("shared.gate/up/down", same form as an
                                     expert) whose output joins the experts' sum scaled by sigmoid("shared.sg" u), a per-token
                                     scalar ("shared.sg": [1][width]); 0 = none */
+  int32_t mask_window;           /* attention: w > 0: position i sees key j iff 0 <= i - j < w (on top of mask_chunk, if both are set); 0: none */
+  float score_softcap;           /* attention: c > 0: score <- c tanh(score / c) after the factor `scale`; 0: none */
+  int32_t ssm_state, ssm_groups; /* DIS_MIX_SSM (with heads, vdim above): state size per head; groups of heads that share B and C */
+  int32_t conv_taps;             /* DIS_MIX_SSM: taps of the convolution over x | B | C (1 .. 16) */
+  int32_t ssm_norm_groups;       /* DIS_MIX_SSM: equal parts of heads * vdim that are normalised separately (0 is read as 1) */
+  uint32_t mlp_flags;            /* DIS_MLP_* */
 } dis_layer_config;
 
 typedef struct dis_stack_config {
@@ -513,6 +541,13 @@ typedef struct dis_stack_config {
    * embedding ("loop.in": [width][2 width], "loop.step": [loop_times][width]). */
   int32_t loop_start, loop_stop, loop_times;
   float logit_softcap;           /* c > 0: logits become c tanh(logits / c) (after logit_scale); 0 = none */
+  uint32_t frame_flags;          /* DIS_FRAME_* */
+  /* Residual streams (needs DIS_FRAME_PRE_NORM).  streams = S > 0: the residual is S vectors x_1 .. x_S per token, all equal to the
+   * embedding at the start.  Sublayer q of a layer (1: mixer, 2: feed-forward) reads u = sum_s "hc<q>.in"[s] x_s, computes
+   * y = f(norm(u)), and every stream becomes x_t <- sum_s "hc<q>.mix"[s][t] x_s + "hc<q>.out"[t] y, all from the old streams.  The
+   * final norm reads the sum of the streams.  0: one residual, x += y. */
+  int32_t streams;
+  float pos_base;                /* DIS_FRAME_POS_SINUS: base of the position vector's frequencies (0 is read as 10000) */
 } dis_stack_config;
 
 /* cfg->model is ignored (model_info reports vocab, width, layers and max_ctx of the stack); tensor parallelism and the

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), n
         assert n in B.PROTOTYPES, f"binding.py lacks a prototype for {n}"
-    assert lib.dis_abi_version() == 4
+    assert lib.dis_abi_version() == 5
 
 
 def test_struct_layout_matches_header(tmp_path):
