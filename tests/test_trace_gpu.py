@@ -40,6 +40,17 @@ def test_trace_replay_of_a_fakonex_model(tmp_path, dtype, tol):
     _replay(tmp_path, dtype, tol, cfg, F.weights(cfg, seed=3), F.oracle_logits)
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", None)])
+def test_trace_replay_of_a_goperax_model(tmp_path, dtype, tol):
+    """The same schedule through a looped Goperax model: windows of 24 and 100 positions against pages of 64, recurrent state and
+    convolution tails of every loop pass handed on from request to request."""
+    from tests import _goperax_util as G
+    cfg = G.config([(G.attention(dim=16, window=24), G.dense()), (G.ssm(), G.moe()), (G.attention(heads=3, kv_heads=3, dim=6, window=100), None),
+                    (G.ssm(heads=2, vdim=16, state=16, groups=1, conv=4, norm_groups=1), G.moe(experts=4, top=1, shared=0))], vocab=90, width=40,
+                   loop=(1, 3, 2))
+    _replay(tmp_path, dtype, tol, cfg, G.weights(cfg, seed=3), G.oracle_logits)
+
+
 def _replay(tmp_path, dtype, tol, cfg, W, oracle_logits):
     model = tmp_path / "model"
     model.mkdir()
