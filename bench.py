@@ -1031,6 +1031,123 @@ def run_fakonex(args):
     return 0
 
 
+def run_goperax(args):
+    """Prefill and decode throughput of Goperax (pre-norm residual streams, a looped stretch of layers, sliding-window attention
+    with soft-capped scores whose values are its keys, a selective state-space mixer, ungated squared-ReLU units dense or as a
+    mixture with a shared unit) next to the closest existing models at equal width, depth, vocabulary and head geometry:
+    Fakonex (the same attention kernels under a chunked mask, the same mixture path), Motolix's parallel layers (the same
+    recurrence kernel in its gated linear attention) and the Llama decoder; random weights, one GPU, measured like --workload
+    fakonex: one pass over `batch` prompts of `prompt_len` tokens, then K decode steps of the batch, timed by the engine's CUDA
+    events around each pass (metadata upload and token read-back included).  Weights exceed L2 at every size."""
+    from distributed_inference_server_b200 import Engine, InferenceParams, ModelShape, WorkerConfig, models
+    from distributed_inference_server_b200.binding import FLAG_NO_GRAPH as B_FLAG_NO_GRAPH
+    sizes = {"w1024": (1024, 4096), "w2048": (2048, 8192)}
+    want = [k for k in (args.sizes.split(",") if args.sizes else sizes) if k in sizes]
+    batch, plen, vocab = args.batch or 8, args.prompt_len, 32000
+    rng = np.random.default_rng(0)
+    out = []
+    clocks = ClockSampler(0)
+    clocks.start()
+    clocks.mark_start()
+    for key in want:
+        W, ff = sizes[key]
+        H = W // 128
+        G = max(1, H // 4)
+        window = max(64, plen // 2)
+        att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+                                              "mask": {"size": window}}}
+        # state-space heads of 64 over an inner width of 2 W, state 128, 8 groups, 4 taps: the usual proportions of such a layer
+        ssm = {"type": "mamba2", "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+        dense = {"kind": "dense", "ff": ff}
+        moe = {"kind": "moe", "expert": {"ff": W}, "router": {"experts": 8, "top": 2}, "shared": {"ff": W}}
+        variants = {"mixed_loop": ([(att, dense), (ssm, moe), (ssm, dense), (att, moe)], (1, 3, 2))}
+        if args.per_mixer:
+            variants["attention"] = ([(att, dense)] * 4, None)
+            variants["ssm"] = ([(ssm, dense)] * 4, None)
+            variants["attention_moe"] = ([(att, moe)] * 4, None)
+        rec = {"size": key, "width": W, "dense_ff": ff, "expert_ff": W, "vocab": vocab, "batch": batch, "prompt_len": plen, "window": window, "streams": 4}
+        prompts = [rng.integers(0, vocab, plen).tolist() for _ in range(batch)]
+        P = InferenceParams(max_tokens=1 << 20, temperature=0.0)
+        ctx = plen + args.steps + args.warmup + 64
+
+        def measure(eng):
+            slots = [eng.seq_add(p, P) for p in prompts]
+            t_pre = []
+            for it in range(1 + max(1, args.ttft_runs)):
+                if it:
+                    for sl in slots:
+                        eng.seq_remove(sl)
+                    slots = [eng.seq_add(p, P) for p in prompts]
+                eng.step(slots, batch * plen)
+                t_pre.append(eng.status().last_step_ms)
+            for _ in range(args.warmup):
+                eng.decode(slots)
+            k0 = eng.status().kernel_launches
+            ms = 0.0
+            for _ in range(args.steps):
+                eng.decode(slots)
+                ms += eng.status().last_step_ms
+            launches = eng.status().kernel_launches - k0
+            for sl in slots:
+                eng.seq_remove(sl)
+            pre = min(t_pre[1:])
+            return {"prefill_ms": round(pre, 3), "prefill_tokens_per_s": round(batch * plen / pre * 1e3, 1),
+                    "decode_ms_per_step": round(ms / args.steps, 4), "decode_tokens_per_s": round(batch * args.steps / ms * 1e3, 1),
+                    "launches_per_decode_step": launches // max(1, args.steps)}
+
+        def stack_engine(spec):
+            eng = Engine(WorkerConfig(None, max_batch=batch, max_step_tokens=batch * plen, page_size=64, kv_pages=(batch * ctx + 63) // 64,
+                                      stack=spec, context_size=ctx, compute_dtype="bfloat16", flags=B_FLAG_NO_GRAPH if args.no_graph else 0))
+            for name, a in models.random_tensors(spec, seed=1).items():
+                eng.load_named(name, a)
+            eng.finalize()
+            return eng
+        depths = {4}
+        for vname, (layers, loop) in variants.items():
+            cfg = {"architecture": "Goperax", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": float(W) ** 0.5}, "streams": 4,
+                   "layers": [dict(json.loads(json.dumps(m)), mlp=json.loads(json.dumps(f))) for m, f in layers]}
+            if loop:
+                cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+            spec = models.goperax_spec(cfg)
+            depths.add(len(spec.layer_runs()))
+            eng = stack_engine(spec)
+            rec["goperax_" + vname] = dict(measure(eng), layer_runs=len(spec.layer_runs()))
+            eng.close()
+        if not args.goperax_only:
+            # Fakonex: the same attention kernels (chunked mask of the window's length) and mixture path, norms on both sides
+            f_att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window}}}
+            f_moe = {"kind": "moe", "expert": {"ff": W}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": W}}
+            cfg = {"architecture": "Fakonex", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+                   "layers": [dict(json.loads(json.dumps(f_att)), mlp=f_moe) for _ in range(4)]}
+            eng = stack_engine(models.fakonex_spec(cfg))
+            rec["fakonex_attention_moe"] = measure(eng)
+            eng.close()
+            # Motolix's parallel layers: the recurrence kernel of the state-space mixer in its gated-linear-attention form
+            par = {"type": "parallel", "mixer": {"left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 10000.0, "dims": 128}},
+                                                 "right": {"heads": H, "dim": 64, "vdim": 128, "tau": 8.0, "rank": 32}, "left_scale": 0.7, "right_scale": 0.7}}
+            m_att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 1000000.0, "dims": 64}}}
+            for nm, mx in (("motolix_parallel", par), ("motolix_attention", m_att)):
+                cfg = {"architecture": "Motolix", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": float(W) ** 0.5}, "logit_scale": 0.5,
+                       "layers": [dict(json.loads(json.dumps(mx)), mlp={"kind": "dense", "ff": ff}) for _ in range(4)]}
+                eng = stack_engine(models.motolix_spec(cfg))
+                rec[nm] = measure(eng)
+                eng.close()
+            for depth in sorted(depths):
+                shape = ModelShape(vocab, W, depth, H, G, 128, ff, ctx)
+                eng = Engine(WorkerConfig(shape, max_batch=batch, max_step_tokens=batch * plen, page_size=64, kv_pages=(batch * ctx + 63) // 64 + batch))
+                eng.load_synthetic(1)
+                eng.finalize()
+                rec[f"llama_{depth}_layers"] = measure(eng)
+                eng.close()
+        out.append(rec)
+    clocks.mark_end()
+    line = {"metric": "goperax_vs_closest_models_equal_size", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "dtype": "bf16", "data": "synthetic (random weights, uniform random tokens)", "higher_is_better": True, "sizes": out,
+            "clocks": clocks.stop()}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1049,9 +1166,10 @@ def main():
     ap.add_argument("--nccl-allreduce", action="store_true", help="TP: use NCCL instead of the fused peer-memory exchange (A/B)")
     ap.add_argument("--tp-exchange", choices=["auto", "oneshot", "twoshot", "ll", "wide"], default="auto",
                     help="TP: peer-memory exchange kernel (auto = ll, the flag-in-data row kernel, up to hidden 4096; wide, the same protocol on a (row, column block) grid, above)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "prefix", "kidolorn", "motolix", "fakonex"], help="serving = BASELINE configs[4]; prefix = TTFT with prefix KV reuse (row f2); kidolorn / motolix / fakonex = that layer-list design beside Llama (and its closest layer-list relative) at equal size")
-    ap.add_argument("--sizes", default="", help="kidolorn, motolix, fakonex: comma list out of w1024,w2048 (default both)")
-    ap.add_argument("--per-mixer", action="store_true", help="kidolorn, motolix, fakonex: also four layers of each mixer (fakonex: of each cache / mask arrangement) alone")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "prefix", "kidolorn", "motolix", "fakonex", "goperax"], help="serving = BASELINE configs[4]; prefix = TTFT with prefix KV reuse (row f2); kidolorn / motolix / fakonex / goperax = that layer-list design beside Llama (and its closest layer-list relatives) at equal size")
+    ap.add_argument("--sizes", default="", help="kidolorn, motolix, fakonex, goperax: comma list out of w1024,w2048 (default both)")
+    ap.add_argument("--per-mixer", action="store_true", help="kidolorn, motolix, fakonex, goperax: also four layers of each mixer (fakonex: of each cache / mask arrangement) alone")
+    ap.add_argument("--goperax-only", action="store_true", help="goperax: skip the other models' rows (profiling under ncu)")
     ap.add_argument("--model", default="8b", choices=["8b", "70b"], help="70b = BASELINE configs[3] (TP=8, batch 32)")
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--prefill-budget", type=int, default=0, help="serving: prompt tokens read per scheduler step (0 = library default)")
@@ -1075,6 +1193,8 @@ def main():
         return run_motolix(args)
     if args.workload == "fakonex":
         return run_fakonex(args)
+    if args.workload == "goperax":
+        return run_goperax(args)
     return run_ours(args)
 
 

@@ -15,7 +15,8 @@ __device__ __forceinline__ float silu_(float v) { return v / (1.f + expf(-v)); }
 // row of S), q is multiplied by qscale, no activation.
 // first column of head 0's q, k, v in a row of proj.  hpg > 1: q and k are shared by groups of hpg consecutive heads (head h reads
 // block h / hpg).  dec_head (gated form): the decay is one factor per token and head, dec [T][H], not one per key channel.
-struct LightCols { int q, k, v; int hpg = 1; int dec_head = 0; };
+// vscale (or null): [T][H], a factor per token and head on the values as they are staged.
+struct LightCols { int q, k, v; int hpg = 1; int dec_head = 0; const float *vscale = nullptr; };
 template <bool GATE>
 __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj, long long ld, LightCols col, const float *decay,
                                                               const float *dec, float qscale, float *state, StackSpans sp, float *o, int H,
@@ -44,7 +45,7 @@ __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj,
     }
     for (int j = threadIdx.x; j < dv; j += blockDim.x) {
       const float vv = row[col.v + (long long)h * dv + j];
-      vs[j] = GATE ? vv : silu_(vv);
+      vs[j] = GATE ? (col.vscale ? vv * col.vscale[(long long)(tok0 + t) * H + h] : vv) : silu_(vv);
     }
     __syncthreads();
     for (int j = l; j < dv; j += 32) {
@@ -135,10 +136,12 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
   float *sdst[2];
   int dstride[2];
   float mul[2];
+  bool isv[2];  // the column is a value: it takes the token's vscale
 #pragma unroll
   for (int u = 0; u < 2; u++) {
     const int c = threadIdx.x + u * 256;
     src[u] = nullptr; sstride[u] = ld; sdst[u] = qs; dstride[u] = DP; mul[u] = 1.f;
+    isv[u] = GATE && col.vscale && c >= 2 * d && c < 2 * d + dv;
     if (c < d) { src[u] = proj + col.q + (long long)(h / col.hpg) * d + c; sdst[u] = qs + c; mul[u] = GATE ? qscale : 1.f; }
     else if (c < 2 * d) { src[u] = proj + col.k + (long long)(h / col.hpg) * d + (c - d); sdst[u] = ks + (c - d); }
     else if (c < 2 * d + dv) { src[u] = proj + col.v + (long long)h * dv + (c - 2 * d); sdst[u] = vs + (c - 2 * d); dstride[u] = DVP; }
@@ -156,6 +159,11 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
       if (t < ct) {
         if (src[0]) tmp[2 * t] = src[0][(long long)(first + t0 + t) * sstride[0]];
         if (src[1]) tmp[2 * t + 1] = src[1][(long long)(first + t0 + t) * sstride[1]];
+        if (GATE && (isv[0] || isv[1])) {  // (one address for the whole CTA: a broadcast)
+          const float f = col.vscale[(long long)(first + t0 + t) * H + h];
+          if (isv[0]) tmp[2 * t] *= f;
+          if (isv[1]) tmp[2 * t + 1] *= f;
+        }
       }
     }
   };
@@ -387,14 +395,17 @@ cudaError_t launch_stack_gla(const float *proj, long long ld, int q_off, int k_o
 // ------------------------------------------------------------------------------------------------ state-space mixer
 // The recurrence S = a_t S + B_t (dt_t x_t)^T, o_t = S^T C_t is the gated one above with a decay per token and head, keys B and
 // queries C shared by the heads of a group, and values dt x: the same kernels, their staging told where to read.
-cudaError_t launch_stack_ssd(const float *buf, long long ld_b, int c_off, int b_off, int v_off, int hpg, const float *dec, float *state,
-                             const StackSpans &sp, float *o, int H, int N, int P, float *seg, float *seg_a, int max_len, cudaStream_t st) {
+cudaError_t launch_stack_ssd(const float *buf, long long ld_b, int c_off, int b_off, int v_off, int hpg, const float *dec,
+                             const float *dt, float *state, const StackSpans &sp, float *o, int H, int N, int P, float *seg, float *seg_a,
+                             int max_len, cudaStream_t st) {
   LightCols col{c_off, b_off, v_off};
   col.hpg = hpg < 1 ? 1 : hpg;
   col.dec_head = 1;
+  col.vscale = dt;
   const int d = N, dv = P;
   if (d <= 32 && dv <= 64) return lightning_reg<4, 2, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   if (d <= 64 && dv <= 64) return lightning_reg<8, 2, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 128 && dv <= 64) return lightning_reg<16, 2, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   if (d <= 64 && dv <= 128) return lightning_reg<8, 4, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   if (d <= 128 && dv <= 128) return lightning_reg<16, 4, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   const int threads = 256;
@@ -406,41 +417,55 @@ cudaError_t launch_stack_ssd(const float *buf, long long ld_b, int c_off, int b_
   return cudaGetLastError();
 }
 
-// Convolution, SiLU, step sizes and decays; one block per token.  The input at position p of the sequence comes from the span's
-// own rows of proj or, before the span's start, from the slot's tail (tail[i] holds position pos0 - (taps-1) + i); before the
-// sequence's start it is zero, so a slot that another sequence used before needs no clearing.
+// Convolution and SiLU over the channels x | B | C, step sizes and decays.  grid (token, stretch of channels); a thread takes
+// four neighbouring channels where the layout allows 16-byte accesses (VEC).  The input at position p of the sequence comes from
+// the span's own rows of proj or, before the span's start, from the slot's tail (tail[i] holds position pos0 - (taps-1) + i);
+// before the sequence's start it is zero, so a slot that another sequence used before needs no clearing.  The first block of a
+// token also forms dt = softplus(proj[dt_off + h] + dt_bias[h]) (no clamp) -> dtv [T][H] and the decay exp(-exp(A_log[h]) dt) -> dec.
+// TAIL (passes of single tokens): the thread moves its channels' tail on by one itself, so no second launch is needed.
 constexpr int kConvMaxTaps = 16;
+template <bool VEC, bool TAIL>
 __global__ void __launch_bounds__(256) stack_ssm_conv_kernel(const float *__restrict__ proj, long long ld, int x_off, int dt_off, int C,
-                                                             int H, int P, int taps, const float *__restrict__ cw,
-                                                             const float *__restrict__ cb, const float *__restrict__ vec,
-                                                             const float *__restrict__ cstate, StackSpans sp, float *__restrict__ buf,
-                                                             long long ld_b, float *__restrict__ dec) {
-  extern __shared__ float dts[];  // [H]
+                                                             int H, int taps, const float *__restrict__ cw, const float *__restrict__ cb,
+                                                             const float *__restrict__ vec, float *cstate, StackSpans sp,
+                                                             float *__restrict__ buf, long long ld_b, float *__restrict__ dec,
+                                                             float *__restrict__ dtv) {
+  constexpr int V = VEC ? 4 : 1;
   const int t = blockIdx.x;
   const int s = sp.span[t], tok0 = sp.sp_tok0[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
   const int back_in_span = t - tok0;  // tokens of the span in front of t
   const float *row = proj + (long long)t * ld;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    const float z = row[dt_off + h] + vec[h];
-    const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));  // softplus, no clamp
-    dts[h] = dt;
-    dec[(long long)t * H + h] = expf(-expf(vec[H + h]) * dt);
-  }
-  __syncthreads();
-  const float *tail = cstate + (long long)slot * (taps - 1) * C;
-  const int inner = H * P;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc = cb[c];
-    for (int j = 0; j < taps; j++) {
-      const int back = taps - 1 - j;
-      float v;
-      if (back <= back_in_span) v = row[x_off + c - (long long)back * ld];
-      else v = (pos0 + back_in_span - back >= 0) ? tail[(long long)((taps - 1) - (back - back_in_span)) * C + c] : 0.f;
-      acc = fmaf(cw[(long long)c * taps + j], v, acc);
+  if (blockIdx.y == 0)
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+      const float z = row[dt_off + h] + vec[h];
+      const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+      dtv[(long long)t * H + h] = dt;
+      dec[(long long)t * H + h] = expf(-expf(vec[H + h]) * dt);
     }
-    const float a = silu_(acc);
-    buf[(long long)t * ld_b + c] = a;
-    if (c < inner) buf[(long long)t * ld_b + C + c] = a * dts[c / P];
+  float *tail = cstate + (long long)slot * (taps - 1) * C;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  if (c >= C) return;
+  float acc[V], in[kConvMaxTaps][V];
+#pragma unroll
+  for (int k = 0; k < V; k++) acc[k] = cb[c + k];
+  for (int j = 0; j < taps; j++) {
+    const int back = taps - 1 - j;
+    const float *src = nullptr;
+    if (back <= back_in_span) src = row + x_off + c - (long long)back * ld;
+    else if (pos0 + back_in_span - back >= 0) src = tail + (long long)((taps - 1) - (back - back_in_span)) * C + c;
+    if (VEC) {
+      const float4 v = src ? *reinterpret_cast<const float4 *>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+      in[j][0] = v.x; in[j][V > 1 ? 1 : 0] = v.y; in[j][V > 2 ? 2 : 0] = v.z; in[j][V > 3 ? 3 : 0] = v.w;
+    } else in[j][0] = src ? src[0] : 0.f;
+#pragma unroll
+    for (int k = 0; k < V; k++) acc[k] = fmaf(cw[(long long)(c + k) * taps + j], in[j][k], acc[k]);
+  }
+  if (VEC) *reinterpret_cast<float4 *>(buf + (long long)t * ld_b + c) = make_float4(silu_(acc[0]), silu_(acc[V > 1 ? 1 : 0]), silu_(acc[V > 2 ? 2 : 0]), silu_(acc[V > 3 ? 3 : 0]));
+  else buf[(long long)t * ld_b + c] = silu_(acc[0]);
+  if (TAIL) {  // the span is this one token: tail'[i] = tail[i + 1], tail'[taps - 2] = the token's input
+    for (int j = 0; j + 1 < taps; j++)
+#pragma unroll
+      for (int k = 0; k < V; k++) tail[(long long)j * C + c + k] = in[j + 1][k];
   }
 }
 // The tail moves on to the span's last taps - 1 inputs (a span shorter than that keeps the end of the old tail in front).
@@ -460,13 +485,21 @@ __global__ void stack_ssm_tail_kernel(const float *__restrict__ proj, long long 
     for (int k = 0; k < n; k++) tail[(long long)k * C + c] = nv[k];
   }
 }
-cudaError_t launch_stack_ssm_conv(const float *proj, long long ld, int x_off, int dt_off, int C, int H, int P, int taps, const float *cw,
+cudaError_t launch_stack_ssm_conv(const float *proj, long long ld, int x_off, int dt_off, int C, int H, int taps, const float *cw,
                                   const float *cb, const float *vec, float *cstate, const StackSpans &sp, float *buf, long long ld_b,
-                                  float *dec, cudaStream_t st) {
-  if (taps < 1 || taps > kConvMaxTaps || (size_t)H * 4 > 40 * 1024) return cudaErrorInvalidValue;
+                                  float *dec, float *dtv, cudaStream_t st) {
+  if (taps < 1 || taps > kConvMaxTaps) return cudaErrorInvalidValue;
   if (sp.T <= 0) return cudaSuccess;
-  stack_ssm_conv_kernel<<<sp.T, 256, (size_t)H * sizeof(float), st>>>(proj, ld, x_off, dt_off, C, H, P, taps, cw, cb, vec, cstate, sp, buf, ld_b, dec);
-  if (taps > 1) stack_ssm_tail_kernel<<<dim3(sp.n_spans, (C + 1023) / 1024), 256, 0, st>>>(proj, ld, x_off, cstate, sp, C, taps);
+  const bool v4 = ((C | x_off | (int)(ld & 3) | (int)(ld_b & 3)) & 3) == 0 && reinterpret_cast<uintptr_t>(proj) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(buf) % 16 == 0 && (taps == 1 || reinterpret_cast<uintptr_t>(cstate) % 16 == 0);
+  const bool single = sp.T == sp.n_spans;  // every span one token long
+  const int per = v4 ? 4 : 1;
+  const dim3 grid(sp.T, (C + 256 * per - 1) / (256 * per));
+#define DIS_CONV(V, S) stack_ssm_conv_kernel<V, S><<<grid, 256, 0, st>>>(proj, ld, x_off, dt_off, C, H, taps, cw, cb, vec, cstate, sp, buf, ld_b, dec, dtv)
+  if (single && taps > 1) { if (v4) DIS_CONV(true, true); else DIS_CONV(false, true); }
+  else { if (v4) DIS_CONV(true, false); else DIS_CONV(false, false); }
+#undef DIS_CONV
+  if (taps > 1 && !single) stack_ssm_tail_kernel<<<dim3(sp.n_spans, (C + 1023) / 1024), 256, 0, st>>>(proj, ld, x_off, cstate, sp, C, taps);
   return cudaGetLastError();
 }
 

@@ -472,8 +472,8 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       name(pre + "mix.o", &L.w_o, 0, {W, inner}, i);
       max_mix = std::max(max_mix, (size_t)inner);
       max_act = std::max(max_act, (size_t)inner);
-      max_ssm = std::max(max_ssm, (size_t)C + inner);
-      max_dec = std::max(max_dec, (size_t)H);
+      max_ssm = std::max(max_ssm, (size_t)C);
+      max_dec = std::max(max_dec, (size_t)2 * H);  // decays, then step sizes
     } else if (lc.mixer == DIS_MIX_MINGRU) {
       const int n = lc.width;
       name(pre + "mix.z", &L.w_in, 0, {n, W}, i);
@@ -1266,13 +1266,14 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       n_mix = H * dv;
     } else if (lc.mixer == DIS_MIX_SSM) {
       const int H = lc.heads, P = lc.vdim, Ns = lc.ssm_state, G = lc.ssm_groups, C = L.conv_ch, inner = H * P;
-      const long long ld_b = (long long)C + inner;  // x | B | C | dt x
+      const long long ld_b = C;  // x | B | C
+      float *dtv = M.dec + (size_t)T * H;  // the step sizes follow the decays
       const float *vec = reinterpret_cast<const float *>(L.ssm_vec.ptr);
-      RET_CUDA(launch_stack_ssm_conv(M.proj, N, L.x_off, L.dt_off, C, H, P, lc.conv_taps, reinterpret_cast<const float *>(L.conv_w.ptr),
-                                     reinterpret_cast<const float *>(L.conv_b.ptr), vec, Rn.conv_state, sp, M.ssm, ld_b, M.dec, stream));
-      kl += lc.conv_taps > 1 ? 2 : 1;
+      RET_CUDA(launch_stack_ssm_conv(M.proj, N, L.x_off, L.dt_off, C, H, lc.conv_taps, reinterpret_cast<const float *>(L.conv_w.ptr),
+                                     reinterpret_cast<const float *>(L.conv_b.ptr), vec, Rn.conv_state, sp, M.ssm, ld_b, M.dec, dtv, stream));
+      kl += lc.conv_taps > 1 && T != sp.n_spans ? 2 : 1;
       const bool segments = M.light_seg && M.light_seg_a && max_span > stack_lightning_seg_tokens() && Ns <= 128 && P <= 128;
-      RET_CUDA(launch_stack_ssd(M.ssm, ld_b, inner + G * Ns, inner, C, H / G, M.dec, Rn.state, sp, M.mix, H, Ns, P, segments ? M.light_seg : nullptr,
+      RET_CUDA(launch_stack_ssd(M.ssm, ld_b, inner + G * Ns, inner, 0, H / G, M.dec, dtv, Rn.state, sp, M.mix, H, Ns, P, segments ? M.light_seg : nullptr,
                                 segments ? M.light_seg_a : nullptr, max_span, stream));
       kl += segments ? 3 : 1;
       RET_CUDA(launch_stack_ssm_out(M.mix, M.ssm, ld_b, M.proj, N, vec + 2 * H, reinterpret_cast<const float *>(L.norm_w.ptr), lc.ssm_norm_groups,

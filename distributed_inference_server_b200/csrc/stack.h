@@ -105,16 +105,17 @@ cudaError_t launch_stack_gla(const float *proj, long long ld, int q_off, int k_o
 // State-space mixer (DIS_MIX_SSM), three steps around the recurrence kernel of gated linear attention.
 // 1. proj [T][ld] holds z | x | B | C | dt as projected.  The C = inner + 2 G N channels from x_off on pass a causal depthwise
 //    convolution over time (cw [C][taps], last tap = the current token; the taps - 1 inputs before a span come from cstate
-//    [slots][taps-1][C], zeros before position 0) plus cb, then SiLU -> buf [T][ld_b] columns 0 .. C (x | B | C).  dt = softplus(
-//    proj[dt_off + h] + vec[h]) (vec = dt_bias | A_log | D, [3H]); buf columns C .. C + inner receive dt * x (the recurrence's
-//    values) and dec [T][H] the decays exp(-exp(A_log[h]) dt).  A second launch moves cstate on to the span's last inputs.
-cudaError_t launch_stack_ssm_conv(const float *proj, long long ld, int x_off, int dt_off, int C, int H, int P, int taps, const float *cw,
+//    [slots][taps-1][C], zeros before position 0) plus cb, then SiLU -> buf [T][ld_b] (x | B | C).  dt = softplus(proj[dt_off + h]
+//    + vec[h]) (vec = dt_bias | A_log | D, [3H]) -> dtv [T][H]; dec [T][H] receives the decays exp(-exp(A_log[h]) dt).  cstate
+//    moves on to the span's last inputs: inside the same launch when every span is one token, else by a second one.
+cudaError_t launch_stack_ssm_conv(const float *proj, long long ld, int x_off, int dt_off, int C, int H, int taps, const float *cw,
                                   const float *cb, const float *vec, float *cstate, const StackSpans &sp, float *buf, long long ld_b,
-                                  float *dec, cudaStream_t st);
-// 2. S [N][P] per head: S = dec[t][h] S + B_t (dt x_t)^T, o_t = S^T C_t.  buf as above (B at b_off, C at c_off, dt x at v_off;
+                                  float *dec, float *dtv, cudaStream_t st);
+// 2. S [N][P] per head: S = dec[t][h] S + B_t (dt[t][h] x_t)^T, o_t = S^T C_t.  buf as above (B at b_off, C at c_off, x at v_off;
 //    head h reads the B, C of group h / hpg); state [slots][H][N][P]; o [T][H*P]; seg / seg_a as for gated linear attention.
-cudaError_t launch_stack_ssd(const float *buf, long long ld_b, int c_off, int b_off, int v_off, int hpg, const float *dec, float *state,
-                             const StackSpans &sp, float *o, int H, int N, int P, float *seg, float *seg_a, int max_len, cudaStream_t st);
+cudaError_t launch_stack_ssd(const float *buf, long long ld_b, int c_off, int b_off, int v_off, int hpg, const float *dec,
+                             const float *dt, float *state, const StackSpans &sp, float *o, int H, int N, int P, float *seg, float *seg_a,
+                             int max_len, cudaStream_t st);
 // 3. y = (o + D[h] x) silu(z), RMS-normed in `parts` equal parts of H*P (each by its own mean square), times w -> out [T][H*P] in
 //    the compute type.  x: buf column 0 on (row stride ld_b), z: proj column 0 on (row stride ld).
 cudaError_t launch_stack_ssm_out(const float *o, const float *buf, long long ld_b, const float *z, long long ld, const float *D,
@@ -307,7 +308,7 @@ struct StackModel {
   StackTensor final_w, final_b;    // layer-norm form of the final norm
   StackTensor loop_in, loop_step;  // [W][2W] compute type, [times][W] fp32
   double *pos_freq = nullptr;      // sinusoidal positions: base^(-2i/W), i < (W + 1) / 2
-  float *ssm = nullptr;            // state-space mixer: x | B | C after convolution and SiLU, then dt x, per token
+  float *ssm = nullptr;            // state-space mixer: x | B | C after convolution and SiLU, per token
   size_t ssm_ld = 0;
   float *x0 = nullptr;             // the scaled embedding rows of the pass (input of every loop pass)
   void *xcat = nullptr;            // [x ; x0] in the compute type
