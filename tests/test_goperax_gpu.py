@@ -161,9 +161,9 @@ def test_attention_over_slices_of_the_history():
         assert U.rel_err(got, want) < F32_TOL if dtype == "float32" else U.bf16_close(got, want)
 
 
-RECURRENCE_SHAPES = {  # (state, vdim): the four register shapes of the recurrence kernel and its shared-memory form
+RECURRENCE_SHAPES = {  # (state, vdim): the register shapes of the recurrence kernel and its shared-memory form
     "state8_vdim40": (8, 40), "state48_vdim64": (48, 64), "state64_vdim96": (64, 96), "state128_vdim128": (128, 128), "state20_vdim136": (20, 136),
-    "state130_vdim8": (130, 8),
+    "state130_vdim8": (130, 8), "state128_vdim64": (128, 64), "state100_vdim48": (100, 48),
 }
 
 
@@ -182,6 +182,41 @@ def test_long_spans_through_the_segments_of_the_recurrence(name):
     f.step([("a", a, 70), ("b", b, 129)])
     f.step([("b", b, 1)])
     assert U.rel_err(f.end("a"), wa) < 5e-5 and U.rel_err(f.end("b"), wb) < 5e-5
+    e.close()
+
+
+CONVOLUTION_SHAPES = {  # (heads, vdim, state, groups, taps): channels heads * vdim + 2 * groups * state
+    "channels_multiple_of_four_taps4": (4, 8, 8, 2, 4), "channels_multiple_of_four_taps7": (2, 6, 6, 1, 7), "channels_odd_taps3": (3, 5, 7, 1, 3),
+    "channels_even_taps2": (3, 6, 4, 1, 2), "over_a_thousand_channels_taps5": (8, 96, 80, 2, 5), "one_tap": (4, 8, 8, 2, 1),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CONVOLUTION_SHAPES))
+def test_convolution_tail_in_prompts_and_single_tokens(name):
+    """The convolution reads four channels at a time where the layout allows it and one otherwise, and moves the slot's tail
+    inside the same launch when every span of the pass is one token: prompts, single tokens and both in turn must agree, in a
+    batch of two whose second sequence starts later (its first tokens see zeros, not the slot's earlier owner)."""
+    H, P, N, G, taps = CONVOLUTION_SHAPES[name]
+    cfg = U.config([(U.ssm(heads=H, vdim=P, state=N, groups=G, conv=taps, norm_groups=1), None), (U.ssm(heads=H, vdim=P, state=N, groups=G, conv=taps, norm_groups=H), U.dense())],
+                   width=40, streams=2)
+    W = U.weights(cfg, seed=5)
+    a, b, c = toks(30, seed=21), toks(19, seed=22), toks(9, seed=23)
+    wa, wb, wc = (U.oracle_logits(cfg, W, x) for x in (a, b, c))
+    e = U.engine(cfg, W, pool_tokens=256, page_size=8, max_batch=2)
+    f = U.Feeder(e)
+    f.step([("a", a, 1)])
+    f.step([("a", a, 1)])
+    f.step([("a", a, 3), ("b", b, 1)])
+    for _ in range(taps + 1):
+        f.step([("a", a, 1), ("b", b, 1)])
+    f.step([("a", a, 2), ("b", b, 18 - taps - 1)])
+    assert U.rel_err(f.end("b"), wb) < F32_TOL
+    f.step([("a", a, 1), ("c", c, 1)])  # c takes the slot that b gave back
+    for _ in range(8):
+        f.step([("a", a, 1), ("c", c, 1)])
+    assert U.rel_err(f.end("c"), wc) < F32_TOL
+    f.step([("a", a, 30 - f.fed["a"])])
+    assert U.rel_err(f.end("a"), wa) < F32_TOL
     e.close()
 
 
