@@ -530,13 +530,17 @@ cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const floa
 // Then, with pre_w: u = sum_s next[s] x_s (next = the coming sublayer's coefficients, their first S numbers; null: u = x_0), and
 // h = u / sqrt(mean(u^2) + eps) * pre_w goes to hc in the compute type.  Everything is fp32.
 constexpr int kHcMaxStreams = 8;
-template <bool F32>
-__global__ void __launch_bounds__(256) stack_boundary_hc_kernel(float *xs, int S, const float *y, int n_part, long long stride,
-                                                                const float *bias, const float *prev, const float *next,
-                                                                const float *pre_w, void *hc, int W, float eps) {
+// SS: the number of streams when the compiler may know it (2, 4), else 0 and S counts at run time up to kHcMaxStreams.
+// VEC: W is a multiple of 4 and every pointer 16-byte aligned, so a thread moves four neighbouring columns per access.
+template <bool F32, int SS, bool VEC>
+__global__ void __launch_bounds__(256) stack_boundary_hc_kernel(float *xs, int S_rt, const float *__restrict__ y, int n_part, long long stride,
+                                                                const float *__restrict__ bias, const float *prev, const float *next,
+                                                                const float *__restrict__ pre_w, void *hc, int W, float eps) {
   extern __shared__ __align__(16) float row[];  // [W]: u
   __shared__ float sh[32];
   __shared__ float cf[2 * kHcMaxStreams + kHcMaxStreams * kHcMaxStreams];  // out[S] | mix[S][S] of prev, then in[S] of next
+  constexpr int V = VEC ? 4 : 1, SM = SS ? SS : kHcMaxStreams;
+  const int S = SS ? SS : S_rt;
   const long long t = blockIdx.x;
   float *xr = xs + t * S * W;
   float *c_out = cf, *c_mix = cf + kHcMaxStreams, *c_in = c_mix + kHcMaxStreams * kHcMaxStreams;
@@ -546,52 +550,111 @@ __global__ void __launch_bounds__(256) stack_boundary_hc_kernel(float *xs, int S
   }
   if (threadIdx.x < S * S) c_mix[threadIdx.x] = prev ? prev[2 * S + threadIdx.x] : (threadIdx.x % (S + 1) == 0 ? 1.f : 0.f);
   __syncthreads();
+  auto ld = [](const float *p, float (&o)[V]) {
+    if (VEC) { const float4 v = *reinterpret_cast<const float4 *>(p); o[0] = v.x; o[V > 1 ? 1 : 0] = v.y; o[V > 2 ? 2 : 0] = v.z; o[V > 3 ? 3 : 0] = v.w; }
+    else o[0] = p[0];
+  };
+  auto st = [](float *p, const float (&o)[V]) {
+    if (VEC) *reinterpret_cast<float4 *>(p) = make_float4(o[0], o[V > 1 ? 1 : 0], o[V > 2 ? 2 : 0], o[V > 3 ? 3 : 0]);
+    else p[0] = o[0];
+  };
   float q = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float old[kHcMaxStreams];
+  for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+    float old[SM][V];
 #pragma unroll
-    for (int k = 0; k < kHcMaxStreams; k++) old[k] = k < S ? xr[(long long)k * W + i] : 0.f;
-    float u = 0.f;
+    for (int k = 0; k < SM; k++) {
+      if (k < S) ld(xr + (long long)k * W + i, old[k]);
+      else {
+#pragma unroll
+        for (int e = 0; e < V; e++) old[k][e] = 0.f;
+      }
+    }
+    float u[V];
+#pragma unroll
+    for (int e = 0; e < V; e++) u[e] = 0.f;
     if (y) {
-      float v = bias ? bias[i] : 0.f;
-      for (int k = 0; k < n_part; k++) v += y[(long long)k * stride + t * W + i];
+      float v[V];
+      if (bias) ld(bias + i, v);
+      else {
 #pragma unroll
-      for (int to = 0; to < kHcMaxStreams; to++) {
+        for (int e = 0; e < V; e++) v[e] = 0.f;
+      }
+      for (int k = 0; k < n_part; k++) {
+        float p[V];
+        ld(y + (long long)k * stride + t * W + i, p);
+#pragma unroll
+        for (int e = 0; e < V; e++) v[e] += p[e];
+      }
+#pragma unroll
+      for (int to = 0; to < SM; to++) {
         if (to < S) {
-          float nv = c_out[to] * v;
+          float nv[V];
 #pragma unroll
-          for (int from = 0; from < kHcMaxStreams; from++)
-            if (from < S) nv = fmaf(c_mix[from * S + to], old[from], nv);
-          xr[(long long)to * W + i] = nv;
-          u = fmaf(c_in[to], nv, u);
+          for (int e = 0; e < V; e++) nv[e] = c_out[to] * v[e];
+#pragma unroll
+          for (int from = 0; from < SM; from++)
+            if (from < S) {
+              const float m = c_mix[from * S + to];
+#pragma unroll
+              for (int e = 0; e < V; e++) nv[e] = fmaf(m, old[from][e], nv[e]);
+            }
+          st(xr + (long long)to * W + i, nv);
+#pragma unroll
+          for (int e = 0; e < V; e++) u[e] = fmaf(c_in[to], nv[e], u[e]);
         }
       }
     } else {
 #pragma unroll
-      for (int k = 0; k < kHcMaxStreams; k++)
-        if (k < S) u = fmaf(c_in[k], old[k], u);
+      for (int k = 0; k < SM; k++)
+        if (k < S) {
+#pragma unroll
+          for (int e = 0; e < V; e++) u[e] = fmaf(c_in[k], old[k][e], u[e]);
+        }
     }
-    row[i] = u;
-    q += u * u;
+    st(row + i, u);
+#pragma unroll
+    for (int e = 0; e < V; e++) q += u[e] * u[e];
   }
   if (!pre_w) return;
   const float r = rsqrtf(block_sum(q, sh) / (float)W + eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(hc, t * W + i, row[i] * r * pre_w[i]);  // each thread re-reads what it wrote itself
+  for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {  // each thread re-reads what it wrote itself
+    float u[V], g[V];
+    ld(row + i, u);
+    ld(pre_w + i, g);
+    if (VEC && !F32) {
+      uint2 o;
+      o.x = (uint32_t)float_to_bf16_bits(u[0] * r * g[0]) | ((uint32_t)float_to_bf16_bits(u[V > 1 ? 1 : 0] * r * g[V > 1 ? 1 : 0]) << 16);
+      o.y = (uint32_t)float_to_bf16_bits(u[V > 2 ? 2 : 0] * r * g[V > 2 ? 2 : 0]) | ((uint32_t)float_to_bf16_bits(u[V > 3 ? 3 : 0] * r * g[V > 3 ? 3 : 0]) << 16);
+      *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(hc) + t * W + i) = o;
+    } else if (VEC) {
+#pragma unroll
+      for (int e = 0; e < V; e++) u[e] = u[e] * r * g[e];
+      st(reinterpret_cast<float *>(hc) + t * W + i, u);
+    } else st_el<F32>(hc, t * W + i, u[0] * r * g[0]);
+  }
+}
+template <bool F32, int SS, bool VEC>
+static cudaError_t boundary_hc_go(float *xs, int streams, const float *y, int n_part, long long stride, const float *bias, const float *prev,
+                                  const float *next, const float *pre_w, void *hc, int T, int W, float eps, cudaStream_t st) {
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_boundary_hc_kernel<F32, SS, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); }));
+  stack_boundary_hc_kernel<F32, SS, VEC><<<T, 256, (size_t)W * 4, st>>>(xs, streams, y, n_part, stride, bias, prev, next, pre_w, hc, W, eps);
+  return cudaGetLastError();
 }
 cudaError_t launch_stack_boundary_hc(float *xs, int streams, const float *y, int n_part, long long stride, const float *bias,
                                      const float *prev, const float *next, const float *pre_w, void *hc, bool f32, int T, int W, float eps,
                                      cudaStream_t st) {
   if (streams < 1 || streams > kHcMaxStreams || (size_t)W * 4 > 160 * 1024) return cudaErrorInvalidValue;
   if (T <= 0) return cudaSuccess;
-  static DeviceOnce once;
-  DIS_CUDA_TRY(once.run([&] {
-    cudaError_t e = cudaFuncSetAttribute(stack_boundary_hc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_boundary_hc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-  }));
-  const size_t shb = (size_t)W * 4;
-  if (f32) stack_boundary_hc_kernel<true><<<T, 256, shb, st>>>(xs, streams, y, n_part < 1 ? 1 : n_part, stride, bias, prev, next, pre_w, hc, W, eps);
-  else stack_boundary_hc_kernel<false><<<T, 256, shb, st>>>(xs, streams, y, n_part < 1 ? 1 : n_part, stride, bias, prev, next, pre_w, hc, W, eps);
-  return cudaGetLastError();
+  if (n_part < 1) n_part = 1;
+  auto al = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec = W % 4 == 0 && stride % 4 == 0 && al(xs) && al(y) && al(bias) && al(pre_w) && al(hc);
+#define DIS_HC(F, SSV, VV) return boundary_hc_go<F, SSV, VV>(xs, streams, y, n_part, stride, bias, prev, next, pre_w, hc, T, W, eps, st)
+#define DIS_HC_S(F, VV) do { if (streams == 2) DIS_HC(F, 2, VV); if (streams == 4) DIS_HC(F, 4, VV); DIS_HC(F, 0, VV); } while (0)
+  if (f32) { if (vec) DIS_HC_S(true, true); else DIS_HC_S(true, false); }
+  else { if (vec) DIS_HC_S(false, true); else DIS_HC_S(false, false); }
+#undef DIS_HC_S
+#undef DIS_HC
 }
 
 __global__ void stack_scale_kernel(float *v, long long n, float s) {

@@ -81,8 +81,13 @@ __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj,
 // and with GATE the product of the segment's decays per channel into `seg_a`; a carry kernel then walks the segments in order,
 // S_in(c+1) = A_c S_in(c) + contribution(c), leaving S_in(c) in `seg`;
 // MODE 2: the segment's outputs, starting from S_in(c).
+// GATE 2 (state-space mixer): one decay per token and head, dec [T][H], and a factor per token and head on the values,
+// col.vscale [T][H]; both are staged as one number per token (the first two entries of the token's decay row), so the inner loop
+// reads them once instead of a vector per group of rows.
+// Rows and columns beyond d and dv: shared memory starts as zeros and nobody writes those entries, so their k, q and decays are
+// zero and their part of S stays zero; the inner loop needs no bounds checks.
 constexpr int kLightTok = 8, kLightSeg = 64;
-template <int RI, int RJ, int MODE, bool GATE>
+template <int RI, int RJ, int MODE, int GATE>
 __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float *__restrict__ proj, long long ld, LightCols col,
                                                                      const float *decay, const float *__restrict__ dec, float qscale,
                                                                      float *state, StackSpans sp, float *__restrict__ o, int H, int d,
@@ -110,12 +115,13 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
   float *vs = ks + kLightTok * DP;             // [tok][DVP]
   float *part = vs + kLightTok * DVP;          // [tok][8][DVP]
   float *as = part + kLightTok * 8 * DVP;      // [tok][DP] (GATE)
+  for (int i = threadIdx.x; i < kLightTok * ((GATE ? 3 : 2) * DP + 9 * DVP); i += blockDim.x) shm[i] = 0.f;  // (the loop's first barrier follows)
   float *st = state + ((long long)slot * H + h) * d * dv;
   const float a = GATE ? 1.f : decay[h];
   float S[RI][RJ];
-  float A[GATE ? RI : 1];  // MODE 1: running product of the decays of this thread's rows
+  float A[GATE == 1 ? RI : 1];  // MODE 1: running product of the decays of this thread's rows (GATE 2: of the head)
 #pragma unroll
-  for (int ii = 0; ii < (GATE ? RI : 1); ii++) A[ii] = 1.f;
+  for (int ii = 0; ii < (GATE == 1 ? RI : 1); ii++) A[ii] = 1.f;
 #pragma unroll
   for (int ii = 0; ii < RI; ii++)
 #pragma unroll
@@ -130,22 +136,24 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
     }
   // Staging: a token's inputs are `per` numbers (q, k, v of this head, and with GATE its d decays); per <= 512, so every thread
   // owns at most two of these columns for all tokens.  Where a column comes from and where it goes is worked out once.
-  const int per = (GATE ? 3 : 2) * d + dv;
+  const int per = GATE == 1 ? 3 * d + dv : 2 * d + dv + (GATE == 2 ? 2 : 0);
   const float *src[2];
   long long sstride[2];
   float *sdst[2];
   int dstride[2];
   float mul[2];
-  bool isv[2];  // the column is a value: it takes the token's vscale
 #pragma unroll
   for (int u = 0; u < 2; u++) {
     const int c = threadIdx.x + u * 256;
     src[u] = nullptr; sstride[u] = ld; sdst[u] = qs; dstride[u] = DP; mul[u] = 1.f;
-    isv[u] = GATE && col.vscale && c >= 2 * d && c < 2 * d + dv;
     if (c < d) { src[u] = proj + col.q + (long long)(h / col.hpg) * d + c; sdst[u] = qs + c; mul[u] = GATE ? qscale : 1.f; }
     else if (c < 2 * d) { src[u] = proj + col.k + (long long)(h / col.hpg) * d + (c - d); sdst[u] = ks + (c - d); }
     else if (c < 2 * d + dv) { src[u] = proj + col.v + (long long)h * dv + (c - 2 * d); sdst[u] = vs + (c - 2 * d); dstride[u] = DVP; }
-    else if (c < per) {  // one decay per key channel, or the head's one decay copied to every channel
+    else if (GATE == 2 && c < per) {  // the head's decay, then the values' factor
+      src[u] = (c == 2 * d + dv ? dec : col.vscale) + h;
+      sstride[u] = H;
+      sdst[u] = as + (c - 2 * d - dv);
+    } else if (c < per) {  // one decay per key channel, or the head's one decay copied to every channel
       src[u] = col.dec_head ? dec + h : dec + (long long)h * d + (c - 2 * d - dv);
       sstride[u] = col.dec_head ? (long long)H : (long long)H * d;
       sdst[u] = as + (c - 2 * d - dv);
@@ -159,11 +167,6 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
       if (t < ct) {
         if (src[0]) tmp[2 * t] = src[0][(long long)(first + t0 + t) * sstride[0]];
         if (src[1]) tmp[2 * t + 1] = src[1][(long long)(first + t0 + t) * sstride[1]];
-        if (GATE && (isv[0] || isv[1])) {  // (one address for the whole CTA: a broadcast)
-          const float f = col.vscale[(long long)(first + t0 + t) * H + h];
-          if (isv[0]) tmp[2 * t] *= f;
-          if (isv[1]) tmp[2 * t + 1] *= f;
-        }
       }
     }
   };
@@ -182,24 +185,24 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
     __syncthreads();
     for (int t = 0; t < ct; t++) {
       float vj[RJ], acc[RJ];
+      const float at = GATE == 2 ? as[t * DP] : a, ft = GATE == 2 ? as[t * DP + 1] : 1.f;
+      if (GATE == 2 && MODE == 1) A[0] *= at;
 #pragma unroll
-      for (int jj = 0; jj < RJ; jj++) { vj[jj] = l + jj * 32 < dv ? vs[t * DVP + l + jj * 32] : 0.f; acc[jj] = 0.f; }
+      for (int jj = 0; jj < RJ; jj++) { vj[jj] = GATE == 2 ? vs[t * DVP + l + jj * 32] * ft : vs[t * DVP + l + jj * 32]; acc[jj] = 0.f; }
 #pragma unroll
       for (int i4 = 0; i4 < RI; i4 += 4) {
         const float4 k4 = *reinterpret_cast<const float4 *>(ks + t * DP + i0 + i4);
         const float4 q4 = *reinterpret_cast<const float4 *>(qs + t * DP + i0 + i4);
-        float4 a4 = make_float4(a, a, a, a);
-        if (GATE) a4 = *reinterpret_cast<const float4 *>(as + t * DP + i0 + i4);
+        float4 a4 = make_float4(at, at, at, at);
+        if (GATE == 1) a4 = *reinterpret_cast<const float4 *>(as + t * DP + i0 + i4);
         const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w}, av[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-          if (i0 + i4 + u < d) {
-            if (GATE && MODE == 1) A[GATE ? i4 + u : 0] *= av[u];
+          if (GATE == 1 && MODE == 1) A[GATE == 1 ? i4 + u : 0] *= av[u];
 #pragma unroll
-            for (int jj = 0; jj < RJ; jj++) {
-              S[i4 + u][jj] = fmaf(av[u], S[i4 + u][jj], kv[u] * vj[jj]);
-              if (MODE != 1) acc[jj] = fmaf(S[i4 + u][jj], qv[u], acc[jj]);
-            }
+          for (int jj = 0; jj < RJ; jj++) {
+            S[i4 + u][jj] = fmaf(av[u], S[i4 + u][jj], kv[u] * vj[jj]);
+            if (MODE != 1) acc[jj] = fmaf(S[i4 + u][jj], qv[u], acc[jj]);
           }
         }
       }
@@ -231,7 +234,7 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
   if (GATE && MODE == 1 && l == 0) {
 #pragma unroll
     for (int ii = 0; ii < RI; ii++)
-      if (i0 + ii < d) sga[i0 + ii] = A[GATE ? ii : 0];
+      if (i0 + ii < d) sga[i0 + ii] = A[GATE == 1 ? ii : 0];
   }
 }
 
@@ -290,7 +293,7 @@ size_t stack_lightning_seg_decay_floats(int cap_tokens, int max_spans, int H, in
   return (size_t)(cap_tokens / kLightSeg + max_spans + 1) * H * d;
 }
 
-template <int RI, int RJ, bool GATE>
+template <int RI, int RJ, int GATE>
 static cudaError_t lightning_reg(const float *proj, long long ld, LightCols col, const float *decay, const float *dec, float qscale,
                                  float *state, const StackSpans &sp, float *o, int H, int d, int dv, float *seg, float *seg_a,
                                  int max_len, cudaStream_t st) {
@@ -403,11 +406,11 @@ cudaError_t launch_stack_ssd(const float *buf, long long ld_b, int c_off, int b_
   col.dec_head = 1;
   col.vscale = dt;
   const int d = N, dv = P;
-  if (d <= 32 && dv <= 64) return lightning_reg<4, 2, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
-  if (d <= 64 && dv <= 64) return lightning_reg<8, 2, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
-  if (d <= 128 && dv <= 64) return lightning_reg<16, 2, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
-  if (d <= 64 && dv <= 128) return lightning_reg<8, 4, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
-  if (d <= 128 && dv <= 128) return lightning_reg<16, 4, true>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 32 && dv <= 64) return lightning_reg<4, 2, 2>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 64 && dv <= 64) return lightning_reg<8, 2, 2>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 128 && dv <= 64) return lightning_reg<16, 2, 2>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 64 && dv <= 128) return lightning_reg<8, 4, 2>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 128 && dv <= 128) return lightning_reg<16, 4, 2>(buf, ld_b, col, nullptr, dec, 1.f, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   const int threads = 256;
   const size_t sh = ((size_t)d * dv + 3 * d + dv + (size_t)(threads / 32) * dv) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;
@@ -468,6 +471,78 @@ __global__ void __launch_bounds__(256) stack_ssm_conv_kernel(const float *__rest
       for (int k = 0; k < V; k++) tail[(long long)j * C + c + k] = in[j + 1][k];
   }
 }
+// The same for passes with prompts, 2 to 4 taps: a block takes kConvTile consecutive tokens and a stretch of channels, a thread
+// keeps its channels' weights and the last TAPS - 1 inputs in registers and reads every input once; the window is fetched anew
+// (from the rows before, the slot's tail or zeros, as above) at the tile's first token and wherever a new span starts.  The
+// products are summed in the order of the kernel above, so a position's result does not depend on which of the two ran.
+constexpr int kConvTile = 16;
+template <int TAPS, bool VEC>
+__global__ void __launch_bounds__(256) stack_ssm_conv_tile_kernel(const float *__restrict__ proj, long long ld, int x_off, int dt_off, int C,
+                                                                  int H, const float *__restrict__ cw, const float *__restrict__ cb,
+                                                                  const float *__restrict__ vec, const float *__restrict__ cstate,
+                                                                  StackSpans sp, float *__restrict__ buf, long long ld_b,
+                                                                  float *__restrict__ dec, float *__restrict__ dtv) {
+  constexpr int V = VEC ? 4 : 1;
+  const int t0 = blockIdx.x * kConvTile, t1 = min(sp.T, t0 + kConvTile);
+  if (blockIdx.y == 0)
+    for (int e = threadIdx.x; e < (t1 - t0) * H; e += blockDim.x) {
+      const int t = t0 + e / H, h = e % H;
+      const float z = proj[(long long)t * ld + dt_off + h] + vec[h];
+      const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+      dtv[(long long)t * H + h] = dt;
+      dec[(long long)t * H + h] = expf(-expf(vec[H + h]) * dt);
+    }
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  if (c >= C) return;
+  auto ldv = [](const float *p, float (&o)[V]) {
+    if (VEC) { const float4 v = *reinterpret_cast<const float4 *>(p); o[0] = v.x; o[V > 1 ? 1 : 0] = v.y; o[V > 2 ? 2 : 0] = v.z; o[V > 3 ? 3 : 0] = v.w; }
+    else o[0] = p[0];
+  };
+  float w[TAPS][V], b[V], win[TAPS - 1][V];
+#pragma unroll
+  for (int k = 0; k < V; k++) {
+    b[k] = cb[c + k];
+#pragma unroll
+    for (int j = 0; j < TAPS; j++) w[j][k] = cw[(long long)(c + k) * TAPS + j];
+  }
+  int prev_span = -1;
+  for (int t = t0; t < t1; t++) {
+    const int s = sp.span[t];
+    const float *row = proj + (long long)t * ld + x_off + c;
+    if (s != prev_span) {
+      prev_span = s;
+      const int back_in_span = t - sp.sp_tok0[s], pos0 = sp.sp_pos0[s];
+      const float *tail = cstate + (long long)sp.sp_slot[s] * (TAPS - 1) * C + c;
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; j++) {
+        const int back = TAPS - 1 - j;
+        if (back <= back_in_span) ldv(row - (long long)back * ld, win[j]);
+        else if (pos0 + back_in_span - back >= 0) ldv(tail + (long long)((TAPS - 1) - (back - back_in_span)) * C, win[j]);
+        else {
+#pragma unroll
+          for (int k = 0; k < V; k++) win[j][k] = 0.f;
+        }
+      }
+    }
+    float cur[V], acc[V];
+    ldv(row, cur);
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+      acc[k] = b[k];
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; j++) acc[k] = fmaf(w[j][k], win[j][k], acc[k]);
+      acc[k] = silu_(fmaf(w[TAPS - 1][k], cur[k], acc[k]));
+    }
+    if (VEC) *reinterpret_cast<float4 *>(buf + (long long)t * ld_b + c) = make_float4(acc[0], acc[V > 1 ? 1 : 0], acc[V > 2 ? 2 : 0], acc[V > 3 ? 3 : 0]);
+    else buf[(long long)t * ld_b + c] = acc[0];
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+#pragma unroll
+      for (int j = 0; j + 1 < TAPS - 1; j++) win[j][k] = win[j + 1][k];
+      win[TAPS - 2][k] = cur[k];
+    }
+  }
+}
 // The tail moves on to the span's last taps - 1 inputs (a span shorter than that keeps the end of the old tail in front).
 __global__ void stack_ssm_tail_kernel(const float *__restrict__ proj, long long ld, int x_off, float *cstate, StackSpans sp, int C,
                                       int taps) {
@@ -496,8 +571,14 @@ cudaError_t launch_stack_ssm_conv(const float *proj, long long ld, int x_off, in
   const int per = v4 ? 4 : 1;
   const dim3 grid(sp.T, (C + 256 * per - 1) / (256 * per));
 #define DIS_CONV(V, S) stack_ssm_conv_kernel<V, S><<<grid, 256, 0, st>>>(proj, ld, x_off, dt_off, C, H, taps, cw, cb, vec, cstate, sp, buf, ld_b, dec, dtv)
+#define DIS_CONV_TILE(TP, V) stack_ssm_conv_tile_kernel<TP, V><<<tgrid, 256, 0, st>>>(proj, ld, x_off, dt_off, C, H, cw, cb, vec, cstate, sp, buf, ld_b, dec, dtv)
+  const dim3 tgrid((sp.T + kConvTile - 1) / kConvTile, grid.y);
   if (single && taps > 1) { if (v4) DIS_CONV(true, true); else DIS_CONV(false, true); }
+  else if (!single && taps == 2) { if (v4) DIS_CONV_TILE(2, true); else DIS_CONV_TILE(2, false); }
+  else if (!single && taps == 3) { if (v4) DIS_CONV_TILE(3, true); else DIS_CONV_TILE(3, false); }
+  else if (!single && taps == 4) { if (v4) DIS_CONV_TILE(4, true); else DIS_CONV_TILE(4, false); }
   else { if (v4) DIS_CONV(true, false); else DIS_CONV(false, false); }
+#undef DIS_CONV_TILE
 #undef DIS_CONV
   if (taps > 1 && !single) stack_ssm_tail_kernel<<<dim3(sp.n_spans, (C + 1023) / 1024), 256, 0, st>>>(proj, ld, x_off, cstate, sp, C, taps);
   return cudaGetLastError();

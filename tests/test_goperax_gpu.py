@@ -479,7 +479,10 @@ def test_other_sizes(dtype, width, vocab, streams, loop):
     t = toks(75, vocab=vocab, seed=10)
     want = U.oracle_logits(cfg, W, t)
     got = U.run_portions(cfg, W, t, [33, 2, 1, 1, 30, 8], dtype, page_size=16, pool_tokens=128)
-    assert U.rel_err(got, want) < F32_TOL if dtype == "float32" else U.bf16_close(got, want)
+    if dtype == "float32":
+        assert U.rel_err(got, want) < 5e-5, U.row_errs(got, want)  # seven layer runs of odd sizes
+    else:
+        assert U.bf16_close(got, want)
 
 
 def test_model_folder_round_trip(tmp_path):
