@@ -156,7 +156,15 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           }
         } else {
           tmem_ld_wait();
-          if (n < N) {
+          if (n < N && out_act) {  // ungated unit: the square of relu, rounded to bf16 for the product that follows
+            uint16_t *o = out_act + (size_t)(t0 + c) * N + n;
+#pragma unroll
+            for (int jj = 0; jj < 32; jj++)
+              if (t0 + c + jj < T) {
+                const float r = fmaxf(__uint_as_float(g[jj]), 0.f);
+                o[(size_t)jj * N] = float_to_bf16_bits(r * r);
+              }
+          } else if (n < N) {
             float *o = out_f32 + (size_t)(t0 + c) * N + n;
 #pragma unroll
             for (int jj = 0; jj < 32; jj++)
@@ -365,6 +373,14 @@ cudaError_t launch_gemm_persist_partial(const TmaMap &w_map, const TmaMap &x_map
                                         int w_row0, cudaStream_t st) {
   if (T <= 0) return cudaSuccess;
   return persist_launch<256, false>(w_map, x_map256, out, nullptr, T, N, K, w_row0, 0, st);
+}
+
+// The same product with the epilogue of an ungated unit: act[t][n] = bf16(relu(sum)^2).
+cudaError_t launch_gemm_persist_relu2(const TmaMap &w_map, const TmaMap &x_map256, uint16_t *act, int T, int N, int K, int w_row0,
+                                      cudaStream_t st) {
+  if (T <= 0) return cudaSuccess;
+  if (!act) return cudaErrorInvalidValue;
+  return persist_launch<256, false>(w_map, x_map256, nullptr, act, T, N, K, w_row0, 0, st);
 }
 
 // w_map64: 64-row boxes over the fused [2I][K] weight (gate rows, then up rows); x_map256: 256-row boxes.

@@ -585,42 +585,92 @@ cudaError_t launch_stack_ssm_conv(const float *proj, long long ld, int x_off, in
 }
 
 // y = (o + D[h] x) silu(z), then each of `parts` equal stretches of the row is divided by its own root mean square, times w.
-// One block per token, the row in shared memory.
-template <bool F32>
+// One block per token, the row in shared memory.  VEC: four neighbouring columns per access (P and the stretch are multiples
+// of 4).  With at least as many stretches as warps a warp normalises a stretch on its own; else the block takes them in turn.
+template <bool F32, bool VEC>
 __global__ void __launch_bounds__(256) stack_ssm_out_kernel(const float *__restrict__ o, const float *__restrict__ buf, long long ld_b,
                                                             const float *__restrict__ z, long long ld, const float *__restrict__ D,
                                                             const float *__restrict__ w, int parts, void *__restrict__ out, int H, int P,
                                                             float eps) {
-  extern __shared__ float yrow[];  // [H*P]
+  extern __shared__ __align__(16) float yrow[];  // [H*P]
   __shared__ float sh[32];
+  constexpr int V = VEC ? 4 : 1;
+  auto ldv = [](const float *p, float (&v)[V]) {
+    if (VEC) { const float4 f = *reinterpret_cast<const float4 *>(p); v[0] = f.x; v[V > 1 ? 1 : 0] = f.y; v[V > 2 ? 2 : 0] = f.z; v[V > 3 ? 3 : 0] = f.w; }
+    else v[0] = p[0];
+  };
   const long long t = blockIdx.x;
   const int inner = H * P, per = inner / parts;
-  for (int i = threadIdx.x; i < inner; i += blockDim.x) {
-    const float y = fmaf(D[i / P], buf[t * ld_b + i], o[t * inner + i]);
-    yrow[i] = y * silu_(z[t * ld + i]);
+  for (int i = threadIdx.x * V; i < inner; i += blockDim.x * V) {
+    float ov[V], xv[V], zv[V];
+    ldv(o + t * inner + i, ov);
+    ldv(buf + t * ld_b + i, xv);
+    ldv(z + t * ld + i, zv);
+    const float Dh = D[i / P];
+#pragma unroll
+    for (int k = 0; k < V; k++) yrow[i + k] = fmaf(Dh, xv[k], ov[k]) * silu_(zv[k]);
   }
   __syncthreads();
+  auto put = [&](int i, float r) {  // columns i .. i + V - 1 of the row, normalised
+    float yv[V], wv[V];
+    ldv(yrow + i, yv);
+    ldv(w + i, wv);
+    if (VEC && !F32) {
+      uint2 pk;
+      pk.x = (uint32_t)float_to_bf16_bits(yv[0] * r * wv[0]) | ((uint32_t)float_to_bf16_bits(yv[V > 1 ? 1 : 0] * r * wv[V > 1 ? 1 : 0]) << 16);
+      pk.y = (uint32_t)float_to_bf16_bits(yv[V > 2 ? 2 : 0] * r * wv[V > 2 ? 2 : 0]) | ((uint32_t)float_to_bf16_bits(yv[V > 3 ? 3 : 0] * r * wv[V > 3 ? 3 : 0]) << 16);
+      *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(out) + t * inner + i) = pk;
+    } else if (VEC) {
+      *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + t * inner + i) =
+          make_float4(yv[0] * r * wv[0], yv[V > 1 ? 1 : 0] * r * wv[V > 1 ? 1 : 0], yv[V > 2 ? 2 : 0] * r * wv[V > 2 ? 2 : 0], yv[V > 3 ? 3 : 0] * r * wv[V > 3 ? 3 : 0]);
+    } else st_el<F32>(out, t * inner + i, yv[0] * r * wv[0]);
+  };
+  const int wp = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (parts >= nw) {
+    for (int g = wp; g < parts; g += nw) {
+      float q = 0.f;
+      for (int i = l * V; i < per; i += 32 * V) {
+        float yv[V];
+        ldv(yrow + g * per + i, yv);
+#pragma unroll
+        for (int k = 0; k < V; k++) q += yv[k] * yv[k];
+      }
+      const float r = rsqrtf(warp_sum(q) / (float)per + eps);
+      for (int i = l * V; i < per; i += 32 * V) put(g * per + i, r);
+    }
+    return;
+  }
   for (int g = 0; g < parts; g++) {
     float q = 0.f;
-    for (int i = threadIdx.x; i < per; i += blockDim.x) { const float v = yrow[g * per + i]; q += v * v; }
+    for (int i = threadIdx.x * V; i < per; i += blockDim.x * V) {
+      float yv[V];
+      ldv(yrow + g * per + i, yv);
+#pragma unroll
+      for (int k = 0; k < V; k++) q += yv[k] * yv[k];
+    }
     const float r = rsqrtf(block_sum(q, sh) / (float)per + eps);
-    for (int i = threadIdx.x; i < per; i += blockDim.x) st_el<F32>(out, t * inner + g * per + i, yrow[g * per + i] * r * w[g * per + i]);
+    for (int i = threadIdx.x * V; i < per; i += blockDim.x * V) put(g * per + i, r);
   }
+}
+template <bool F32, bool VEC>
+static cudaError_t ssm_out_go(const float *o, const float *buf, long long ld_b, const float *z, long long ld, const float *D, const float *w,
+                              int parts, void *out, int T, int H, int P, float eps, cudaStream_t st) {
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_ssm_out_kernel<F32, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); }));
+  stack_ssm_out_kernel<F32, VEC><<<T, 256, (size_t)H * P * 4, st>>>(o, buf, ld_b, z, ld, D, w, parts, out, H, P, eps);
+  return cudaGetLastError();
 }
 cudaError_t launch_stack_ssm_out(const float *o, const float *buf, long long ld_b, const float *z, long long ld, const float *D,
                                  const float *w, int parts, void *out, bool f32, int T, int H, int P, float eps, cudaStream_t st) {
   const int inner = H * P;
   if (parts < 1 || inner % parts || (size_t)inner * 4 > 160 * 1024) return cudaErrorInvalidValue;
   if (T <= 0) return cudaSuccess;
-  static DeviceOnce once;
-  DIS_CUDA_TRY(once.run([&] {
-    cudaError_t e = cudaFuncSetAttribute(stack_ssm_out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_ssm_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-  }));
-  const size_t shb = (size_t)inner * 4;
-  if (f32) stack_ssm_out_kernel<true><<<T, 256, shb, st>>>(o, buf, ld_b, z, ld, D, w, parts, out, H, P, eps);
-  else stack_ssm_out_kernel<false><<<T, 256, shb, st>>>(o, buf, ld_b, z, ld, D, w, parts, out, H, P, eps);
-  return cudaGetLastError();
+  auto al = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec = P % 4 == 0 && (inner / parts) % 4 == 0 && ld % 4 == 0 && ld_b % 4 == 0 && al(o) && al(buf) && al(z) && al(w) && al(out);
+  if (f32) return vec ? ssm_out_go<true, true>(o, buf, ld_b, z, ld, D, w, parts, out, T, H, P, eps, st)
+                      : ssm_out_go<true, false>(o, buf, ld_b, z, ld, D, w, parts, out, T, H, P, eps, st);
+  return vec ? ssm_out_go<false, true>(o, buf, ld_b, z, ld, D, w, parts, out, T, H, P, eps, st)
+             : ssm_out_go<false, false>(o, buf, ld_b, z, ld, D, w, parts, out, T, H, P, eps, st);
 }
 
 // out[t][off + h*dv + j] = scale * o[t][h][j] / rms(o[t][h]) * w[j] * silu(gate[t][h*dv + j]): the norm runs over one head's dv

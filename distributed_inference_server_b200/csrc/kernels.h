@@ -115,6 +115,9 @@ int gemm_pick_tile_rows(int N);
 bool gemm_use_persist(int T, int N, bool dual);
 cudaError_t launch_gemm_persist_partial(const TmaMap &w_map128, const TmaMap &x_map256, float *out, int T, int N, int K,
                                         int w_row0, cudaStream_t st);
+// the same product, its epilogue writing bf16(relu(sum)^2) (an ungated unit's activation) instead of the fp32 sums
+cudaError_t launch_gemm_persist_relu2(const TmaMap &w_map128, const TmaMap &x_map256, uint16_t *act, int T, int N, int K, int w_row0,
+                                      cudaStream_t st);
 cudaError_t launch_gemm_persist_silu(const TmaMap &w_map64, const TmaMap &x_map256, uint16_t *act, int T, int I, int K,
                                      int w_row0, cudaStream_t st);
 cudaError_t launch_gemm_persist_glu(const TmaMap &w_map64, const TmaMap &x_map256, uint16_t *act, int T, int I, int K,

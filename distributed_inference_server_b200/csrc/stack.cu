@@ -1216,6 +1216,15 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       kl++;
       return gemm(cur_act, f32, ff, w_down, 0, nullptr, out, T, W, ff, cap_tokens, nullptr, later_ok);
     }
+    // an ungated unit in prompt-sized bf16 passes: the persistent product's epilogue squares the relu and writes bf16
+    if (stack_tc && stack_persist && !f32 && act_kind == DIS_ACT_RELU2 && !b_gu.ptr && W % 8 == 0 && !w_gu.f32 && gemm_use_persist(T, ff, false)) {
+      const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, 256);
+      const TmaMap *wm = stack_map(w_gu.ptr, (uint64_t)ff, (uint64_t)W, 128);
+      if (!xm || !wm) return cudaErrorInvalidValue;
+      RET_CUDA(launch_gemm_persist_relu2(*wm, *xm, reinterpret_cast<uint16_t *>(cur_act), T, ff, W, 0, cur_st));
+      kl++;
+      return gemm(cur_act, f32, ff, w_down, 0, nullptr, out, T, W, ff, cap_tokens, nullptr, later_ok);
+    }
     // the gated unit sums the slices of its input product itself and adds the bias the product left out
     const float *gu_bias = nullptr;
     RET_CUDA(gemm(M.hc, f32, W, w_gu, 0, reinterpret_cast<const float *>(b_gu.ptr), cur_proj, T, gu_rows * ff, W, cap_tokens, &gu_bias, true));

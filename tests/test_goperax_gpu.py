@@ -245,6 +245,33 @@ def test_large_passes_take_the_tensor_core_expert_products(monkeypatch):
     assert U.bf16_close(res[0], res[1], tol=3e-2)
 
 
+def test_wide_dense_unit_in_a_prompt_pass_squares_the_relu_in_the_product(monkeypatch):
+    """2048 prompt tokens through a dense unit of 4736 columns in bfloat16: enough tiles for the persistent tensor-core
+    product, whose epilogue then writes relu(.)^2 in bfloat16 itself.  Against the oracle at a few positions, and against the
+    same pass with that kernel switched off (DIS_STACK_PERSIST=0: product, then the activation kernel), which rounds the same
+    operands and the same activations."""
+    cfg = U.config([(U.ssm(heads=2, vdim=8, state=8, groups=1), U.dense(ff=4736)), (U.attention(heads=2, kv_heads=1, dim=16, window=40), U.dense(ff=4736))],
+                   width=64, vocab=64, streams=2)
+    W = U.weights(cfg, seed=29)
+    seqs = [toks(512, vocab=64, seed=90 + i) for i in range(4)]
+    want = np.concatenate([U.oracle_logits(cfg, W, sq[:131])[[7, 130]] for sq in seqs])
+    res = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("DIS_STACK_PERSIST", flag)
+        e = U.engine(cfg, W, "bfloat16", max_batch=4, pool_tokens=4 * 512, page_size=64, max_step_tokens=4 * 512, rows=64)
+        P = InferenceParams(max_tokens=1 << 20, temperature=0.0)
+        slots = [e.seq_add(sq, P) for sq in seqs]
+        for sl in slots:
+            e.seq_probe(sl, [7, 130, 300])
+        e.step(slots)
+        res.append(e.last_logits(e.last_logit_rows()).copy())
+        e.close()
+    assert res[0].shape == (4 * 4, 64)
+    first_two = [4 * i + j for i in range(4) for j in (0, 1)]
+    assert U.bf16_close(res[0][first_two], want) and U.bf16_close(res[1][first_two], want)
+    assert U.bf16_close(res[0], res[1], tol=3e-2)
+
+
 def test_batches_of_unequal_requests_against_each_alone():
     cfg = U.config(STACK, loop=LOOP)
     W = U.weights(cfg, seed=13)
