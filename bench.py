@@ -1054,7 +1054,7 @@ def run_goperax(args):
         H = W // 128
         G = max(1, H // 4)
         window = max(64, plen // 2)
-        att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+        att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
                                               "mask": {"size": window}}}
         # state-space heads of 64 over an inner width of 2 W, state 128, 8 groups, 4 taps: the usual proportions of such a layer
         ssm = {"type": "mamba2", "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
@@ -1104,7 +1104,7 @@ def run_goperax(args):
             return eng
         depths = {4}
         for vname, (layers, loop) in variants.items():
-            cfg = {"architecture": "Goperax", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": float(W) ** 0.5}, "streams": 4,
+            cfg = {"architecture": "Goperax", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": float(W) ** 0.5}, "streams": 4,
                    "layers": [dict(json.loads(json.dumps(m)), mlp=json.loads(json.dumps(f))) for m, f in layers]}
             if loop:
                 cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
