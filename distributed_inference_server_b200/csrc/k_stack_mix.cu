@@ -1,6 +1,7 @@
 // k_stack_mix.cu -- the token mixers of the layer-list decoders: the decayed linear-attention scan, the minimal gated recurrence,
 // and latent attention (query absorption happens in a batched matrix product in stack.cu; here: rotary + cache write, and the
 // attention itself over the paged latents).  States and scores are fp32.
+#include <cstdlib>
 #include "stack_dev.cuh"
 
 namespace dis {
@@ -286,6 +287,26 @@ __global__ void stack_lightning_carry_kernel(const float *decay, const float *se
 }
 
 int stack_lightning_seg_tokens() { return kLightSeg; }
+// Whether a pass should cut its long spans into segments.  Walking a span in one piece costs its length times three
+// operations per state element, once per wave of (span, head) CTAs (two fit an SM); the segments cost five operations per
+// element (contributions, then outputs) over all segment CTAs in waves, plus the carry.  Many sequences with many heads fill
+// the GPU without segments and then pay less; a single long prompt needs them.
+bool stack_lightning_segmented(int n_spans, int T, int H, int max_len) {
+  if (max_len <= kLightSeg) return false;
+  const char *force = getenv("DIS_STACK_LIGHT_SEGMENTS");  // 2: always cut (tests)
+  if (force && atoi(force) == 2) return true;
+  static int slots = 0;
+  if (!slots) {
+    int dev = 0, n_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1) n_sm = 148;
+    slots = 2 * n_sm;
+  }
+  const long long pairs = (long long)n_spans * H;
+  const long long whole = (long long)max_len * ((pairs + slots - 1) / slots) * 3;
+  const long long seg_ctas = ((long long)T / kLightSeg + n_spans) * H;
+  const long long cut = ((seg_ctas + slots - 1) / slots) * kLightSeg * 5 + kLightSeg;
+  return cut < whole;
+}
 size_t stack_lightning_seg_floats(int cap_tokens, int max_spans, int H, int d, int dv) {
   return (size_t)(cap_tokens / kLightSeg + max_spans + 1) * H * d * dv;
 }

@@ -1266,7 +1266,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       const int H = lc.heads, d = lc.dim, dv = lc.vdim;
       int max_len = 0;
       for (auto &sh : stack_spans_h) max_len = std::max(max_len, sh.len);
-      const bool segments = M.light_seg && max_len > stack_lightning_seg_tokens() && d <= 128 && dv <= 128;
+      const bool segments = M.light_seg && stack_lightning_segmented(sp.n_spans, T, H, max_len) && d <= 128 && dv <= 128;
       RET_CUDA(launch_stack_lightning(M.proj, N, reinterpret_cast<const float *>(L.decay_d.ptr), Rn.state, sp, M.mix, H, d, dv,
                                       segments ? M.light_seg : nullptr, max_len, stream));
       if (segments) kl += 2;
@@ -1281,7 +1281,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       RET_CUDA(launch_stack_ssm_conv(M.proj, N, L.x_off, L.dt_off, C, H, lc.conv_taps, reinterpret_cast<const float *>(L.conv_w.ptr),
                                      reinterpret_cast<const float *>(L.conv_b.ptr), vec, Rn.conv_state, sp, M.ssm, ld_b, M.dec, dtv, stream));
       kl += lc.conv_taps > 1 && T != sp.n_spans ? 2 : 1;
-      const bool segments = M.light_seg && M.light_seg_a && max_span > stack_lightning_seg_tokens() && Ns <= 128 && P <= 128;
+      const bool segments = M.light_seg && M.light_seg_a && stack_lightning_segmented(sp.n_spans, T, H, max_span) && Ns <= 128 && P <= 128;
       RET_CUDA(launch_stack_ssd(M.ssm, ld_b, inner + G * Ns, inner, 0, H / G, M.dec, dtv, Rn.state, sp, M.mix, H, Ns, P, segments ? M.light_seg : nullptr,
                                 segments ? M.light_seg_a : nullptr, max_span, stream));
       kl += segments ? 3 : 1;
@@ -1319,7 +1319,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
         const int Hr = lc.gla_heads, dr = lc.gla_dim, dvr = lc.gla_vdim;
         RET_CUDA(launch_stack_gla_decay(M.proj, N, L.ga_off, L.a2.ptr, L.a2.f32, reinterpret_cast<const float *>(L.a2_b.ptr), T, Hr * dr,
                                         lc.gla_rank, lc.gla_tau, M.dec, stream));
-        const bool segments = M.light_seg && M.light_seg_a && max_span > stack_lightning_seg_tokens();
+        const bool segments = M.light_seg && M.light_seg_a && stack_lightning_segmented(sp.n_spans, T, Hr, max_span);
         RET_CUDA(launch_stack_gla(M.proj, N, L.gq_off, L.gk_off, L.gv_off, M.dec, Rn.state, sp, M.mix, Hr, dr, dvr,
                                   segments ? M.light_seg : nullptr, segments ? M.light_seg_a : nullptr, max_span, stream));
         RET_CUDA(launch_stack_headnorm_silu(M.mix, reinterpret_cast<const float *>(L.gla_norm.ptr), M.proj + L.gg_off, N, M.act, L.n_act,

@@ -90,6 +90,8 @@ cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long
 // longest span of the pass) are then cut into segments that run side by side, with a carry pass between them.
 size_t stack_lightning_seg_floats(int cap_tokens, int max_spans, int H, int d, int dv);
 int stack_lightning_seg_tokens();
+// whether a pass of n_spans spans (T tokens, the longest max_len) over H heads is faster cut into segments than span by span
+bool stack_lightning_segmented(int n_spans, int T, int H, int max_len);
 cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
                                    float *o, int H, int d, int dv, float *seg, int max_len, cudaStream_t st);
 // Gated linear attention (per-channel decay): S = diag(a_t) S + k_t v_t^T, o_t = S^T (q_t / sqrt(d)).

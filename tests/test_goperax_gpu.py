@@ -220,6 +220,25 @@ def test_convolution_tail_in_prompts_and_single_tokens(name):
     e.close()
 
 
+@pytest.mark.parametrize("force", ["1", "2"])
+def test_many_heads_and_sequences_walk_long_spans_whole(monkeypatch, force):
+    """Four prompts of 100 tokens over 40 heads fill the GPU span by span, so the pass walks each span in one piece although
+    it is longer than a segment; DIS_STACK_LIGHT_SEGMENTS=2 cuts it all the same.  Both agree with the oracle, and a second
+    portion continues either."""
+    monkeypatch.setenv("DIS_STACK_LIGHT_SEGMENTS", force)
+    cfg = U.config([(U.ssm(heads=40, vdim=4, state=4, groups=5, conv=2, norm_groups=4), None)], width=24, streams=0)
+    W = U.weights(cfg, seed=34)
+    seqs = {k: toks(130, seed=50 + k) for k in range(4)}
+    want = {k: U.oracle_logits(cfg, W, v) for k, v in seqs.items()}
+    e = U.engine(cfg, W, pool_tokens=4 * 144, page_size=16, max_batch=4, max_step_tokens=400)
+    f = U.Feeder(e)
+    f.step([(k, seqs[k], 100) for k in seqs])
+    f.step([(k, seqs[k], 30) for k in seqs])
+    for k in seqs:
+        assert U.rel_err(f.end(k), want[k]) < 5e-5
+    e.close()
+
+
 def test_large_passes_take_the_tensor_core_expert_products(monkeypatch):
     """A pass of 1280 prompt tokens in bfloat16: per-expert tensor-core products over rows sorted by expert and the shared unit
     on the tensor cores.  Against the oracle, and against the same pass on the tiled fp32-FMA products (DIS_STACK_TC=0), which
